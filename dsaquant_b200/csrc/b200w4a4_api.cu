@@ -1,0 +1,401 @@
+// C-ABI entry points of libb200w4a4.so (declared in include/b200w4a4.h).
+// Host side only: argument checks, TMA descriptor encoding, kernel launches.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/b200w4a4.h"
+#include "gemm_w4a4.cuh"
+#include "quant_act.cuh"
+#include "weight_pack.cuh"
+
+namespace {
+
+using namespace b200w4a4;
+
+constexpr int kMaxDevices = 64;
+
+// Device status word: kernels write a role code here when a bounded wait runs out.
+__device__ int g_device_status;
+
+std::atomic<int> g_cta_group{0};  // 0 = not chosen yet (environment decides on first use)
+
+struct DeviceState {
+  std::once_flag once;
+  int err = B200W4A4_OK;
+  int sm_count = 0;
+  int* status_ptr = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::once_flag g_encode_once;
+EncodeTiledFn g_encode = nullptr;
+
+EncodeTiledFn get_encode() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  });
+  return g_encode;
+}
+
+// Per-device one-time set-up with that device current: capability check, SM
+// count, address of the status word, shared-memory opt-in of the GEMM kernels.
+int device_state(DeviceState** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B200W4A4_ECUDA;
+  if (dev < 0 || dev >= kMaxDevices) return B200W4A4_EINVAL;
+  DeviceState& st = g_dev[dev];
+  std::call_once(st.once, [&st, dev] {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+      st.err = B200W4A4_ECUDA;
+      return;
+    }
+    if (prop.major != 10 || prop.minor != 0) {
+      st.err = B200W4A4_EARCH;
+      return;
+    }
+    st.sm_count = prop.multiProcessorCount;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) {
+      st.err = B200W4A4_ECUDA;
+      return;
+    }
+    st.status_ptr = static_cast<int*>(p);
+    if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_w4a4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<1>::SMEM_ALLOC) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_w4a4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<2>::SMEM_ALLOC) != cudaSuccess) {
+      st.err = B200W4A4_ECUDA;
+      return;
+    }
+  });
+  *out = &st;
+  return st.err;
+}
+
+int current_cta_group() {
+  int g = g_cta_group.load(std::memory_order_relaxed);
+  if (g == 0) {
+    const char* e = getenv("B200W4A4_CTA_GROUP");
+    g = (e != nullptr && e[0] == '2') ? 2 : 1;
+    g_cta_group.store(g, std::memory_order_relaxed);
+  }
+  return g;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_nk(int N, int K) {
+  if (N < 128 || K < 64) return B200W4A4_ESHAPE;
+  if ((K % 64) != 0 || (N % 128) != 0) return B200W4A4_ESHAPE;
+  return B200W4A4_OK;
+}
+
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner,
+              uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+              CUtensorMapSwizzle sw) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return B200W4A4_ECUDA;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+template <int CG>
+int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
+                const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
+                int N, int K, cudaStream_t stream) {
+  using C = GemmCfg<CG>;
+  CUtensorMap tm_a, tm_w, tm_out;
+  int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, qact, static_cast<uint64_t>(K),
+                     static_cast<uint64_t>(M), static_cast<uint64_t>(K), C::BK, C::BM,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200W4A4_OK) return rc;
+  rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K / 2),
+                 static_cast<uint64_t>(N), static_cast<uint64_t>(K / 2), C::BK / 2, C::B_ROWS,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != B200W4A4_OK) return rc;
+  rc = encode_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, out, static_cast<uint64_t>(N),
+                 static_cast<uint64_t>(M), static_cast<uint64_t>(N) * 2, 64, 32,
+                 CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200W4A4_OK) return rc;
+
+  GemmParams p;
+  p.act_scale = act_scale;
+  p.w_scale = w_scale;
+  p.bias = bias;
+  p.acc_dump = acc_dump;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.m_tiles = (M + C::BM * CG - 1) / (C::BM * CG);
+  p.n_tiles = (N + C::BN - 1) / C::BN;
+  p.status = st.status_ptr;
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  const int groups = st.sm_count / CG;
+  const unsigned grid = static_cast<unsigned>((tiles < groups ? tiles : groups) * CG);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(C::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_ALLOC;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<CG>, tm_a, tm_w, tm_out, p);
+  return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200w4a4_version(void) { return B200W4A4_ABI_VERSION; }
+
+const char* b200w4a4_strerror(int code) {
+  switch (code) {
+    case B200W4A4_OK: return "ok";
+    case B200W4A4_EINVAL: return "invalid argument (null pointer, bad size or enum)";
+    case B200W4A4_ESHAPE: return "unsupported shape (need K % 64 == 0, N % 128 == 0, M >= 1)";
+    case B200W4A4_EALIGN: return "pointer is not 16-byte aligned";
+    case B200W4A4_EARCH: return "device is not compute capability 10.0 (sm_100a required)";
+    case B200W4A4_ECUDA: return "CUDA runtime or driver call failed";
+    case B200W4A4_EWORKSPACE: return "workspace too small";
+    case B200W4A4_EDEVICE: return "a kernel recorded a device-side time-out";
+    default: return "unknown b200w4a4 error code";
+  }
+}
+
+int b200w4a4_query(int device, int* sm_count, int* cc_major, int* cc_minor) {
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    cudaGetLastError();
+    return B200W4A4_ECUDA;
+  }
+  if (sm_count != nullptr) *sm_count = prop.multiProcessorCount;
+  if (cc_major != nullptr) *cc_major = prop.major;
+  if (cc_minor != nullptr) *cc_minor = prop.minor;
+  return (prop.major == 10 && prop.minor == 0) ? B200W4A4_OK : B200W4A4_EARCH;
+}
+
+int b200w4a4_pack_weight(const void* w_f16, const void* ch_scale_f16, void* vdm_packed,
+                         void* vdm_scale_packed, void* vdm_scale, int N, int K, void* stream) {
+  if (w_f16 == nullptr || vdm_packed == nullptr || vdm_scale_packed == nullptr ||
+      vdm_scale == nullptr)
+    return B200W4A4_EINVAL;
+  int rc = check_nk(N, K);
+  if (rc != B200W4A4_OK) return rc;
+  if (!aligned16(w_f16) || !aligned16(vdm_packed)) return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* w = static_cast<const __half*>(w_f16);
+  const __half* scale = static_cast<const __half*>(ch_scale_f16);
+  if (scale == nullptr) {
+    weight_absmax_scale_kernel<<<static_cast<unsigned>(N), 256, 0, s>>>(
+        w, static_cast<__half*>(vdm_scale), N, K);
+    scale = static_cast<const __half*>(vdm_scale);
+  }
+  const size_t words = static_cast<size_t>(N) * K / 8;
+  pack_weight_v1_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, s>>>(
+      w, scale, static_cast<uint32_t*>(vdm_packed), N, K);
+  const size_t nscale = static_cast<size_t>(N) * (K / 64);
+  pack_wscale_v1_kernel<<<static_cast<unsigned>((nscale + 255) / 256), 256, 0, s>>>(
+      scale, static_cast<__half*>(vdm_scale_packed),
+      static_cast<const void*>(scale) == vdm_scale ? nullptr : static_cast<__half*>(vdm_scale), N, K);
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+size_t b200w4a4_repack_bytes(int N, int K) {
+  if (check_nk(N, K) != B200W4A4_OK) return 0;
+  return static_cast<size_t>(N) * (K / 2);
+}
+
+int b200w4a4_repack_weight(const void* vdm_packed, void* w_b200, const void* vdm_scale_packed,
+                           void* w_scale_plain, int N, int K, void* stream) {
+  if (vdm_packed == nullptr || w_b200 == nullptr) return B200W4A4_EINVAL;
+  if ((vdm_scale_packed == nullptr) != (w_scale_plain == nullptr)) return B200W4A4_EINVAL;
+  int rc = check_nk(N, K);
+  if (rc != B200W4A4_OK) return rc;
+  if (!aligned16(vdm_packed) || !aligned16(w_b200)) return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t chunks = static_cast<size_t>(N) * (K / 32);
+  repack_v1_to_b200_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, s>>>(
+      static_cast<const uint32_t*>(vdm_packed), static_cast<uint4*>(w_b200), N, K);
+  if (vdm_scale_packed != nullptr) {
+    unswizzle_wscale_v1_kernel<<<static_cast<unsigned>((N + 255) / 256), 256, 0, s>>>(
+        static_cast<const __half*>(vdm_scale_packed), static_cast<__half*>(w_scale_plain), N, K);
+  }
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+size_t b200w4a4_qact_bytes(int M, int K, int container) {
+  if (M < 1 || K < 64 || (K % 64) != 0) return 0;
+  if (container == B200W4A4_QACT_INT8) return static_cast<size_t>(M) * K;
+  if (container == B200W4A4_QACT_NIBBLE) return static_cast<size_t>(M) * (K / 2);
+  return 0;
+}
+
+int b200w4a4_quantize_act(const void* x, int x_dtype, void* qact, int container, float* act_scale,
+                          int M, int K, float clip, void* stream) {
+  if (x == nullptr || qact == nullptr || act_scale == nullptr) return B200W4A4_EINVAL;
+  if (M < 1 || K < 64 || (K % 64) != 0) return B200W4A4_ESHAPE;
+  if (!(clip > 0.0f)) return B200W4A4_EINVAL;
+  if (!aligned16(x) || !aligned16(qact)) return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaErrorInvalidValue;
+#define B200W4A4_QDISPATCH(T)                                                                     \
+  (container == B200W4A4_QACT_INT8                                                                \
+       ? launch_quant_act<T, QOUT_INT8>(static_cast<const T*>(x), qact, act_scale, M, K, clip, s) \
+       : launch_quant_act<T, QOUT_NIBBLE>(static_cast<const T*>(x), qact, act_scale, M, K, clip, s))
+  if (container != B200W4A4_QACT_INT8 && container != B200W4A4_QACT_NIBBLE) return B200W4A4_EINVAL;
+  switch (x_dtype) {
+    case B200W4A4_F16: e = B200W4A4_QDISPATCH(__half); break;
+    case B200W4A4_BF16: e = B200W4A4_QDISPATCH(__nv_bfloat16); break;
+    case B200W4A4_F32: e = B200W4A4_QDISPATCH(float); break;
+    default: return B200W4A4_EINVAL;
+  }
+#undef B200W4A4_QDISPATCH
+  return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+int b200w4a4_gemm(const void* qact, const float* act_scale, const void* w_b200, const void* w_scale,
+                  const void* bias, void* out, int32_t* acc_dump, int M, int N, int K,
+                  void* stream) {
+  if (qact == nullptr || act_scale == nullptr || w_b200 == nullptr || w_scale == nullptr ||
+      out == nullptr)
+    return B200W4A4_EINVAL;
+  if (M < 1) return B200W4A4_ESHAPE;
+  int rc = check_nk(N, K);
+  if (rc != B200W4A4_OK) return rc;
+  if (!aligned16(qact) || !aligned16(w_b200) || !aligned16(w_scale) || !aligned16(out) ||
+      (bias != nullptr && !aligned16(bias)) || (acc_dump != nullptr && !aligned16(acc_dump)))
+    return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (current_cta_group() == 2)
+    return launch_gemm<2>(*st, qact, act_scale, w_b200, static_cast<const __half*>(w_scale),
+                          static_cast<const __half*>(bias), static_cast<__half*>(out), acc_dump, M,
+                          N, K, s);
+  return launch_gemm<1>(*st, qact, act_scale, w_b200, static_cast<const __half*>(w_scale),
+                        static_cast<const __half*>(bias), static_cast<__half*>(out), acc_dump, M, N,
+                        K, s);
+}
+
+size_t b200w4a4_linear_workspace_bytes(int M, int K) {
+  if (M < 1 || K < 64 || (K % 64) != 0) return 0;
+  const size_t codes = (static_cast<size_t>(M) * K + 255) & ~static_cast<size_t>(255);
+  const size_t scales = (static_cast<size_t>(M) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+  return codes + scales;
+}
+
+int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* w_scale,
+                    const void* bias, void* out, void* workspace, size_t workspace_bytes, int M,
+                    int N, int K, float clip, void* stream) {
+  if (workspace == nullptr) return B200W4A4_EINVAL;
+  const size_t need = b200w4a4_linear_workspace_bytes(M, K);
+  if (need == 0) return B200W4A4_ESHAPE;
+  if (workspace_bytes < need) return B200W4A4_EWORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200W4A4_EALIGN;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* qact = ws;
+  float* act_scale =
+      reinterpret_cast<float*>(ws + ((static_cast<size_t>(M) * K + 255) & ~static_cast<size_t>(255)));
+  int rc = b200w4a4_quantize_act(x, x_dtype, qact, B200W4A4_QACT_INT8, act_scale, M, K, clip, stream);
+  if (rc != B200W4A4_OK) return rc;
+  return b200w4a4_gemm(qact, act_scale, w_b200, w_scale, bias, out, nullptr, M, N, K, stream);
+}
+
+int b200w4a4_unpack_codes(const void* packed, int8_t* codes, int rows, int K, int which,
+                          void* stream) {
+  if (packed == nullptr || codes == nullptr) return B200W4A4_EINVAL;
+  if (rows < 1 || K < 64 || (K % 64) != 0) return B200W4A4_ESHAPE;
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t total = static_cast<size_t>(rows) * K;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  switch (which) {
+    case B200W4A4_CODES_WEIGHT_B200:
+      unpack_b200_weight_kernel<<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(packed), codes,
+                                                     rows, K);
+      break;
+    case B200W4A4_CODES_WEIGHT_V1:
+      if ((rows % 128) != 0) return B200W4A4_ESHAPE;
+      unpack_v1_weight_kernel<<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(packed), codes, rows,
+                                                   K);
+      break;
+    case B200W4A4_CODES_ACT_NIBBLE:
+      unpack_nibble_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(packed), codes,
+                                                     rows, K);
+      break;
+    default:
+      return B200W4A4_EINVAL;
+  }
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+int b200w4a4_set_cta_group(int cta_group) {
+  if (cta_group != 1 && cta_group != 2) return B200W4A4_EINVAL;
+  const int prev = current_cta_group();
+  g_cta_group.store(cta_group, std::memory_order_relaxed);
+  return prev;
+}
+
+int b200w4a4_last_device_status(int device) {
+  int prev = 0;
+  if (cudaGetDevice(&prev) != cudaSuccess) return B200W4A4_ECUDA;
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return B200W4A4_ECUDA;
+  }
+  int rc = B200W4A4_OK;
+  DeviceState* st = nullptr;
+  rc = device_state(&st);
+  int value = 0;
+  if (rc == B200W4A4_OK) {
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(&value, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemset(st->status_ptr, 0, sizeof(int)) != cudaSuccess)
+      rc = B200W4A4_ECUDA;
+  }
+  cudaSetDevice(prev);
+  return rc == B200W4A4_OK ? value : rc;
+}
+
+}  // extern "C"

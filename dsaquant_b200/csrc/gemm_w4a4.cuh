@@ -1,0 +1,478 @@
+// W4A4 GEMM for sm_100a:  out[m,n] = fp16( float(sum_k qa[m,k]*qw[n,k]) * (sa[m]*sw[n]) + bias[n] )
+//
+// Replaces linear_w4a4_kernel of the reference
+// (vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu:627-686, mma.sync m16n8k64 s4 fed
+// from registers) with a persistent, warp-specialised tcgen05 kernel:
+//
+//   warp 0      TMA producer: activation codes (int8 container, K-major, 128B
+//               swizzle) and packed int4 weight tiles (two codes per byte)
+//   warp 1      owns TMEM; one lane issues tcgen05.mma kind::i8 (K=32 slices)
+//   warps 2-5   unpack the int4 weight tile into the int8 K-major/128B-swizzle
+//               tile the tensor core reads (tcgen05 has no s4 kind)
+//   warps 6-9   epilogue: tcgen05.ld the int32 accumulator, dequantise with the
+//               per-token x per-channel scales, add bias, fp16, TMA store
+//
+// Weight nibble convention (produced by the load-time repack, see
+// weight_pack.cuh): inside each 128-wide K block, byte (16*c + i) of a row
+// holds code[k0+32c+i] in its HIGH nibble and code[k0+32c+16+i] in its LOW
+// nibble.  `p & 0xF0F0F0F0` and `(p << 4) & 0xF0F0F0F0` are then two runs of
+// 16 consecutive-k int8 values equal to 16*code: no sign extension is needed.
+// The int32 accumulator comes out multiplied by 16 and the epilogue undoes it
+// with an exact arithmetic shift, so accumulators stay bit-exact.
+//
+// CG == 1: one CTA computes a 128 x 256 tile.  CG == 2: a CTA pair computes a
+// 256 x 256 tile with cta_group::2 MMAs; each CTA stages its own 128 rows of A
+// and unpacks its own 128 weight rows, halving per-SM shared-memory traffic.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace b200w4a4 {
+
+// Device status codes written by a kernel whose bounded wait ran out.
+enum : int {
+  DEV_OK = 0,
+  DEV_TIMEOUT_PRODUCER = 101,
+  DEV_TIMEOUT_UNPACK = 102,
+  DEV_TIMEOUT_MMA = 103,
+  DEV_TIMEOUT_EPILOGUE = 104,
+};
+
+template <int CG>
+struct GemmCfg {
+  static constexpr int BM = 128;                 // rows of A per CTA
+  static constexpr int BN = 256;                 // output columns per tile
+  static constexpr int BK = 128;                 // k per pipeline stage (one 128B swizzle row)
+  static constexpr int B_ROWS = BN / CG;         // weight rows staged + unpacked per CTA
+  static constexpr int A_BYTES = BM * BK;        // int8
+  static constexpr int BP_BYTES = B_ROWS * BK / 2;
+  static constexpr int BU_BYTES = B_ROWS * BK;
+  static constexpr int S1 = (CG == 1) ? 3 : 4;   // TMA ring depth (A + packed B)
+  static constexpr int S2 = (CG == 1) ? 2 : 3;   // unpacked-B ring depth
+  static constexpr int STAGE1 = A_BYTES + BP_BYTES;
+  static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16, per warp, double buffered
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF;
+  static constexpr int OFF_RING1 = 0;
+  static constexpr int OFF_RING2 = OFF_RING1 + S1 * STAGE1;
+  static constexpr int OFF_EPI = OFF_RING2 + S2 * BU_BYTES;
+  static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
+  static constexpr int NUM_BARS = 3 * S1 + 2 * S2 + 4 + 1;
+  static constexpr int SMEM_BYTES = OFF_BAR + 8 * NUM_BARS + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1024 B
+  static constexpr int THREADS = 320;
+  static constexpr int TMEM_COLS = 512;          // two 128 x 256 int32 accumulators
+  static_assert(STAGE1 % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
+  static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
+};
+
+// 64-bit shared-memory matrix descriptor, K-major, 128-byte swizzle, 8-row
+// groups 1024 B apart (bit layout: start>>4 [0,14), LBO>>4 [16,30),
+// SBO>>4 [32,46), version=1 [46,48), layout type 2 = SWIZZLE_128B [61,64)).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// 32-bit instruction descriptor for kind::i8: D=s32 (2 @ bit 4), A=s8 (1 @ bit 7),
+// B=s8 (1 @ bit 10), both K-major, N>>3 @ bit 17, M>>4 @ bit 24.
+__host__ __device__ constexpr uint32_t make_i8_idesc(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+struct GemmParams {
+  const float* act_scale;   // [M] fp32
+  const __half* w_scale;    // [N] fp16
+  const __half* bias;       // [N] fp16 or null
+  int32_t* acc_dump;        // [M,N] int32 or null (tests)
+  int M, N, K;
+  int m_tiles, n_tiles;     // in units of (CG*128) rows and 256 columns
+  int* status;              // device status word
+};
+
+namespace detail {
+
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+
+// Bounded wait on an mbarrier phase.  On time-out records `code` once, raises
+// the CTA-local abort flag and returns false; every other role sees the flag
+// (or the global status word) in its own wait and drains too.
+template <bool CLUSTER>
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                         int* status, int code) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    bool ok = CLUSTER ? ptx::mbar_test_cluster(bar, parity) : ptx::mbar_test(bar, parity);
+    if (ok) return true;
+    if ((++spins & 0x3FF) == 0) {
+      if (*abort_flag) return false;
+      if (*reinterpret_cast<volatile int*>(status) != 0) {
+        *abort_flag = 1;
+        return false;
+      }
+      uint64_t now = ptx::globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        atomicCAS(status, 0, code);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+}  // namespace detail
+
+template <int CG>
+__global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                 const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+  using C = GemmCfg<CG>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles want a 1024 B aligned base.
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? detail::cluster_ctarank() : 0u;
+  const bool leader = (cta_rank == 0);
+
+  // ---- barrier map ---------------------------------------------------------
+  const uint32_t bar0 = smem_base + C::OFF_BAR;
+  auto bar_tma_full = [&](int s) { return bar0 + 8u * s; };                       // A (+Bp when CG==1)
+  auto bar_bp_full = [&](int s) { return bar0 + 8u * (C::S1 + s); };              // packed B (CG==2)
+  auto bar_ring1_free = [&](int s) { return bar0 + 8u * (2 * C::S1 + s); };       // MMA + unpackers done
+  auto bar_bu_full = [&](int s) { return bar0 + 8u * (3 * C::S1 + s); };
+  auto bar_bu_free = [&](int s) { return bar0 + 8u * (3 * C::S1 + C::S2 + s); };
+  auto bar_acc_full = [&](int b) { return bar0 + 8u * (3 * C::S1 + 2 * C::S2 + b); };
+  auto bar_acc_free = [&](int b) { return bar0 + 8u * (3 * C::S1 + 2 * C::S2 + 2 + b); };
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(smem_gen + C::OFF_BAR + 8 * (C::NUM_BARS - 1));
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::S1; ++s) {
+      ptx::mbar_init(bar_tma_full(s), 1);
+      ptx::mbar_init(bar_bp_full(s), 1);
+      ptx::mbar_init(bar_ring1_free(s), 1 + 4);   // one MMA commit + four unpack warps
+    }
+    for (int s = 0; s < C::S2; ++s) {
+      ptx::mbar_init(bar_bu_full(s), 4 * CG);     // unpack warps of every CTA in the group
+      ptx::mbar_init(bar_bu_free(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(bar_acc_full(b), 1);
+      ptx::mbar_init(bar_acc_free(b), 4 * CG);    // epilogue warps of every CTA in the group
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&tm_a);
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_out);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CG>(ptx::smem_u32(tmem_holder), C::TMEM_COLS);
+    ptx::tmem_relinquish<CG>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) detail::cluster_sync_all();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  // ---- persistent tile loop bookkeeping -----------------------------------
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int first_tile = static_cast<int>(blockIdx.x) / CG;
+  const int tile_step = static_cast<int>(gridDim.x) / CG;
+  const int kblocks = (p.K + C::BK - 1) / C::BK;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
+        const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+        const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM;
+        const int n0 = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::S1;
+          const uint32_t ph = (it / C::S1) & 1;
+          if (!detail::wait_bar<CG == 2>(bar_ring1_free(s), ph ^ 1, abort_flag, p.status,
+                                         DEV_TIMEOUT_PRODUCER)) {
+            alive = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + C::OFF_RING1 + s * C::STAGE1;
+          const uint32_t bp_dst = a_dst + C::A_BYTES;
+          if constexpr (CG == 1) {
+            ptx::mbar_arrive_expect_tx(bar_tma_full(s), C::A_BYTES + C::BP_BYTES);
+            ptx::tma_load_2d(a_dst, &tm_a, bar_tma_full(s), kb * C::BK, m0);
+            ptx::tma_load_2d(bp_dst, &tm_w, bar_tma_full(s), kb * (C::BK / 2), n0);
+          } else {
+            // A halves of both CTAs are consumed by the leader's MMA: credit the leader's barrier.
+            if (leader) ptx::mbar_arrive_expect_tx(bar_tma_full(s), 2 * C::A_BYTES);
+            ptx::tma_load_2d_pair(a_dst, &tm_a, ptx::mapa(bar_tma_full(s), 0), kb * C::BK, m0);
+            ptx::mbar_arrive_expect_tx(bar_bp_full(s), C::BP_BYTES);
+            ptx::tma_load_2d(bp_dst, &tm_w, bar_bp_full(s), kb * (C::BK / 2), n0);
+          }
+        }
+      }
+      if (!alive) {
+        // Drain: give loads already issued a bounded time to land before smem goes away.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0 && (CG == 1 || leader)) {
+      constexpr uint32_t idesc = make_i8_idesc(C::BM * CG, C::BN);
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool alive = true;
+      for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
+        const uint32_t ab = local_tile & 1;
+        const uint32_t aph = (local_tile >> 1) & 1;
+        if (!detail::wait_bar<CG == 2>(bar_acc_free(ab), aph ^ 1, abort_flag, p.status,
+                                       DEV_TIMEOUT_MMA)) {
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + ab * C::BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s1 = it % C::S1, s2 = it % C::S2;
+          const uint32_t ph1 = (it / C::S1) & 1, ph2 = (it / C::S2) & 1;
+          if (!detail::wait_bar<CG == 2>(bar_tma_full(s1), ph1, abort_flag, p.status,
+                                         DEV_TIMEOUT_MMA) ||
+              !detail::wait_bar<CG == 2>(bar_bu_full(s2), ph2, abort_flag, p.status,
+                                         DEV_TIMEOUT_MMA)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint64_t adesc =
+              make_kmajor_sw128_desc(smem_base + C::OFF_RING1 + s1 * C::STAGE1);
+          const uint64_t bdesc =
+              make_kmajor_sw128_desc(smem_base + C::OFF_RING2 + s2 * C::BU_BYTES);
+#pragma unroll
+          for (int k = 0; k < C::BK / 32; ++k) {
+            // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
+            ptx::mma_i8_ss<CG>(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          if constexpr (CG == 1) {
+            ptx::mma_commit(bar_ring1_free(s1));
+            ptx::mma_commit(bar_bu_free(s2));
+          } else {
+            ptx::mma_commit_pair(bar_ring1_free(s1), 0x3);
+            ptx::mma_commit_pair(bar_bu_free(s2), 0x3);
+          }
+        }
+        if (alive) {
+          if constexpr (CG == 1)
+            ptx::mma_commit(bar_acc_full(ab));
+          else
+            ptx::mma_commit_pair(bar_acc_full(ab), 0x3);
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ===================== int4 -> int8 weight unpack =====================
+    const int tid_u = static_cast<int>(threadIdx.x) - 64;  // 0..127
+    const uint32_t row_x = static_cast<uint32_t>((tid_u >> 2) & 7);
+    const uint32_t c2 = static_cast<uint32_t>(tid_u & 3) * 2;
+    const uint32_t hi_off = ((c2 ^ row_x) << 4);
+    const uint32_t lo_off = (((c2 + 1) ^ row_x) << 4);
+    uint32_t it = 0;
+    bool alive = true;
+    for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s1 = it % C::S1, s2 = it % C::S2;
+        const uint32_t ph1 = (it / C::S1) & 1, ph2 = (it / C::S2) & 1;
+        const uint32_t full_bar = (CG == 1) ? bar_tma_full(s1) : bar_bp_full(s1);
+        if (!detail::wait_bar<false>(full_bar, ph1, abort_flag, p.status, DEV_TIMEOUT_UNPACK) ||
+            !detail::wait_bar<CG == 2>(bar_bu_free(s2), ph2 ^ 1, abort_flag, p.status,
+                                       DEV_TIMEOUT_UNPACK)) {
+          alive = false;
+          break;
+        }
+        const uint32_t bp = smem_base + C::OFF_RING1 + s1 * C::STAGE1 + C::A_BYTES;
+        const uint32_t bu = smem_base + C::OFF_RING2 + s2 * C::BU_BYTES;
+#pragma unroll
+        for (int j = 0; j < C::B_ROWS * 4 / 128; ++j) {
+          const int q = tid_u + 128 * j;          // 16-byte packed chunk index in the tile
+          const uint4 pk = detail::lds128(bp + 16u * q);
+          uint4 hi, lo;
+          hi.x = pk.x & 0xF0F0F0F0u; lo.x = (pk.x << 4) & 0xF0F0F0F0u;
+          hi.y = pk.y & 0xF0F0F0F0u; lo.y = (pk.y << 4) & 0xF0F0F0F0u;
+          hi.z = pk.z & 0xF0F0F0F0u; lo.z = (pk.z << 4) & 0xF0F0F0F0u;
+          hi.w = pk.w & 0xF0F0F0F0u; lo.w = (pk.w << 4) & 0xF0F0F0F0u;
+          const uint32_t row_addr = bu + 128u * static_cast<uint32_t>(q >> 2);
+          detail::sts128(row_addr + hi_off, hi);
+          detail::sts128(row_addr + lo_off, lo);
+        }
+        // Generic-proxy writes must be visible to the tensor core's async-proxy reads.
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(bar_ring1_free(s1));
+          if constexpr (CG == 1)
+            ptx::mbar_arrive(bar_bu_full(s2));
+          else
+            ptx::mbar_arrive_cluster(bar_bu_full(s2), 0);
+        }
+      }
+    }
+  } else {
+    // ===================== epilogue =====================
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const uint32_t stage_base = smem_base + C::OFF_EPI + (warp - 6) * 2 * C::EPI_BUF;
+    const uint32_t row_sw = static_cast<uint32_t>(lane & 7);
+    uint32_t local_tile = 0;
+    uint32_t store_it = 0;
+    bool alive = true;
+    for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
+      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM + quad * 32;
+      const int n0 = nt * C::BN;
+      const uint32_t ab = local_tile & 1;
+      const uint32_t aph = (local_tile >> 1) & 1;
+      if (!detail::wait_bar<CG == 2>(bar_acc_full(ab), aph, abort_flag, p.status,
+                                     DEV_TIMEOUT_EPILOGUE)) {
+        alive = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const int row = m0 + lane;
+      const float sa = (row < p.M) ? __ldg(p.act_scale + row) : 0.0f;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * C::BN;
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; ++c) {
+        uint32_t acc[32];
+        ptx::tmem_ld_32x32(taddr + 32u * c, acc);
+        ptx::tmem_ld_wait();
+        if (c == C::BN / 32 - 1) {
+          // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CG == 1)
+              ptx::mbar_arrive(bar_acc_free(ab));
+            else
+              ptx::mbar_arrive_cluster(bar_acc_free(ab), 0);
+          }
+        }
+        const int col0 = n0 + 32 * c;
+        const bool cols_valid = col0 < p.N;  // N is a multiple of 128: a 32-chunk is all in or all out
+        if ((c & 1) == 0) {
+          // Staging buffer reuse: the TMA store issued two groups ago must have read it.
+          if (lane == 0) ptx::tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        const uint32_t stage = stage_base + (store_it & 1) * C::EPI_BUF + 128u * lane;
+        if (cols_valid) {
+          if (p.acc_dump != nullptr && row < p.M) {
+            int4* dst = reinterpret_cast<int4*>(p.acc_dump + static_cast<size_t>(row) * p.N + col0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              dst[i] = make_int4(static_cast<int>(acc[4 * i]) >> 4, static_cast<int>(acc[4 * i + 1]) >> 4,
+                                 static_cast<int>(acc[4 * i + 2]) >> 4,
+                                 static_cast<int>(acc[4 * i + 3]) >> 4);
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint4 wsv = __ldg(reinterpret_cast<const uint4*>(p.w_scale + col0 + 8 * g));
+            uint4 bv = make_uint4(0, 0, 0, 0);
+            if (p.bias != nullptr) bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + 8 * g));
+            const __half2* ws2 = reinterpret_cast<const __half2*>(&wsv);
+            const __half2* b2 = reinterpret_cast<const __half2*>(&bv);
+            uint32_t packed[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float2 wsf = __half22float2(ws2[h]);
+              const float2 bf = __half22float2(b2[h]);
+              // (acc16 >> 4) is exact: every weight byte was 16 * code.
+              const float a0 = static_cast<float>(static_cast<int>(acc[8 * g + 2 * h]) >> 4);
+              const float a1 = static_cast<float>(static_cast<int>(acc[8 * g + 2 * h + 1]) >> 4);
+              float v0 = __fmul_rn(a0, __fmul_rn(sa, wsf.x));
+              float v1 = __fmul_rn(a1, __fmul_rn(sa, wsf.y));
+              if (p.bias != nullptr) {
+                v0 = __fadd_rn(v0, bf.x);
+                v1 = __fadd_rn(v1, bf.y);
+              }
+              const __half2 o = __floats2half2_rn(v0, v1);
+              packed[h] = *reinterpret_cast<const uint32_t*>(&o);
+            }
+            const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + g);
+            detail::sts128(stage + ((chunk ^ row_sw) << 4),
+                           make_uint4(packed[0], packed[1], packed[2], packed[3]));
+          }
+        }
+        if ((c & 1) == 1) {
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (col0 - 32 < p.N && m0 < p.M)
+              ptx::tma_store_2d(&tm_out, stage_base + (store_it & 1) * C::EPI_BUF, col0 - 32, m0);
+            ptx::tma_store_commit();
+          }
+          ++store_it;
+        }
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+  }
+
+  // ---- teardown --------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) detail::cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace b200w4a4

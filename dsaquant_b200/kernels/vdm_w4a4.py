@@ -1,0 +1,428 @@
+"""B200 (sm_100a) implementation of the DSAQuant W4A4 kernel wrapper.
+
+Drop-in for the reference module vdm_infer/kernels/vdm_w4a4.py: same public
+names, argument order, defaults and error types
+(build_config / is_available / load_error :115-179, pack_weight_with_scale
+:209-214, quantize_weight_per_channel :217-219, linear_vdm_w4a4 :222-244,
+quantize_activation_per_token :247-250, linear_prequantized :253-256,
+linear_vdm_w4a4_qkv :259-298).  The work is done by libb200w4a4.so through its
+C ABI; there is no Triton, no other backend and no CPU fallback: without the
+library (or without a compute-capability-10.0 device) every op raises.
+
+Behavioural notes for callers of the reference module:
+
+* `qweight` / `wscales` are still the vdm_w4a4_packed_v1 buffers
+  (`vdm_weight_packed` [N,K/2] u8, `vdm_weight_scale_packed` [N,K/64] f16).  On
+  first use each pair is repacked once into the layout the tcgen05 GEMM stages
+  with TMA, plus the plain per-channel scale [N]; the result is cached per
+  tensor object and dropped when the tensor is garbage collected.
+* `x` is read as it is (fp16, bf16 or fp32) instead of through an fp16 copy
+  (vdm_w4a4.py:182-184); for fp16 callers the result is the same.
+* Activation scales stay fp32 end to end, and codes use true IEEE division, so
+  codes and accumulators are bit-identical to the reference's PyTorch W4A4 path.
+* `quantize_activation_per_token` / `linear_prequantized` keep their signatures
+  but exchange this library's activation container: int8 codes [M,K] (one code
+  per byte, no padding of M to 256) and fp32 scales [M].
+"""
+from __future__ import annotations
+
+import os
+import weakref
+from pathlib import Path
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from ..csrc import build as _build
+
+BLOCK_M = 256
+BLOCK_N = 128
+WARP_K = 64
+
+_DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+QACT_INT8 = 0
+QACT_NIBBLE = 1
+
+_SM100_ALIASES = {
+    "b200": "10.0a", "blackwell": "10.0a", "sm100": "10.0a", "sm100a": "10.0a",
+    "sm_100": "10.0a", "sm_100a": "10.0a", "10.0": "10.0a", "10.0a": "10.0a",
+}
+
+
+# --------------------------------------------------------------------------- build / arch selection
+def _configure_cuda_home() -> None:
+    if os.environ.get("CUDA_HOME"):
+        return
+    if Path("/usr/local/cuda").exists():
+        os.environ["CUDA_HOME"] = "/usr/local/cuda"
+
+
+def _detect_arch_list() -> str:
+    """Same precedence as the reference (TORCH_CUDA_ARCH_LIST, then VDM_W4A4_TARGET_ARCH alias,
+    then the visible device), with the sm_100a aliases added and 10.0a as the fallback."""
+    explicit = os.environ.get("TORCH_CUDA_ARCH_LIST")
+    if explicit:
+        return explicit
+    target = os.environ.get("VDM_W4A4_TARGET_ARCH", "auto").strip().lower()
+    if target in _SM100_ALIASES:
+        return _SM100_ALIASES[target]
+    if torch.cuda.is_available():
+        major, minor = torch.cuda.get_device_capability()
+        return "10.0a" if (major, minor) == (10, 0) else f"{major}.{minor}"
+    return "10.0a"
+
+
+def _arch_tag(arch_list: str) -> str:
+    tags = []
+    for token in arch_list.replace(";", " ").replace(",", " ").split():
+        ptx = "+ptx" in token.lower()
+        token = token.lower().replace("+ptx", "")
+        if token.startswith("sm_"):
+            tag = "sm" + token[3:]
+        elif "." in token:
+            major, minor = token.split(".", 1)
+            tag = f"sm{major}{minor}"
+        else:
+            tag = token.replace("-", "_")
+        tags.append(tag + ("ptx" if ptx else ""))
+    return "_".join(tags) if tags else "sm100a"
+
+
+def build_config() -> dict:
+    _configure_cuda_home()
+    arch_list = _detect_arch_list()
+    tag = _arch_tag(arch_list)
+    return {
+        "cuda_home": os.environ.get("CUDA_HOME"),
+        "torch_cuda": torch.version.cuda,
+        "arch_list": arch_list,
+        "arch_tag": tag,
+        "build_dir": str(_build.lib_path().parent),
+        "extension_name": os.environ.get("VDM_W4A4_EXT_NAME", _build.LIB_NAME),
+    }
+
+
+def _load_ext():
+    tag = _arch_tag(_detect_arch_list())
+    if "sm100a" not in tag.split("_") and "sm100" not in tag.split("_"):
+        raise RuntimeError(f"b200 W4A4 kernels target sm_100a only, selected arch is {tag!r}")
+    _configure_cuda_home()
+    return _lib.load()
+
+
+def is_available() -> bool:
+    try:
+        _load_ext()
+        return True
+    except BaseException:
+        return False
+
+
+def load_error() -> Optional[BaseException]:
+    return _lib.load_error()
+
+
+# --------------------------------------------------------------------------- helpers
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (the W4A4 path has no CPU fallback)")
+
+
+def _as_2d_contiguous(x: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, ...]]:
+    orig_shape = tuple(x.shape[:-1])
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.dtype not in _DTYPE_CODE:
+        x2 = x2.float()
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if x2.data_ptr() % 16 != 0:
+        x2 = x2.clone()
+    return x2, orig_shape
+
+
+def _check_linear_shapes(x_2d: torch.Tensor, qweight: torch.Tensor, wscales: torch.Tensor) -> None:
+    if x_2d.shape[1] % WARP_K != 0:
+        raise ValueError(f"K={x_2d.shape[1]} must be a multiple of {WARP_K}")
+    if qweight.shape[0] % BLOCK_N != 0:
+        raise ValueError(f"N={qweight.shape[0]} must be a multiple of {BLOCK_N}")
+    if qweight.shape[1] != x_2d.shape[1] // 2:
+        raise ValueError("qweight shape must be [N, K/2]")
+    if wscales.shape != (qweight.shape[0], x_2d.shape[1] // WARP_K):
+        raise ValueError("wscales shape must be [N, K/64]")
+
+
+class _DeviceGuard:
+    """Makes `device` current for the duration of a call when it is not already."""
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+# --------------------------------------------------------------------------- weight side
+def pack_weight_with_scale(weight: torch.Tensor, channel_scale: torch.Tensor):
+    """fp weight [N,K] + caller-provided per-channel scale -> the three vdm_w4a4_packed_v1
+    buffers (qweight u8 [N,K/2], packed_scales f16 [N,K/64], channel_scales f16 [N])."""
+    lib = _load_ext()
+    _require_cuda(weight, "weight")
+    weight_h = weight.detach().half().contiguous()
+    scale_h = channel_scale.detach().reshape(-1).half().contiguous().to(weight_h.device)
+    return _pack(lib, weight_h, scale_h)
+
+
+def quantize_weight_per_channel(weight: torch.Tensor):
+    lib = _load_ext()
+    _require_cuda(weight, "weight")
+    return _pack(lib, weight.detach().half().contiguous(), None)
+
+
+def _pack(lib, weight_h: torch.Tensor, scale_h: Optional[torch.Tensor]):
+    if weight_h.dim() != 2:
+        raise RuntimeError("weight must be [N, K]")
+    n, k = weight_h.shape
+    if scale_h is not None and scale_h.numel() != n:
+        raise RuntimeError("channel_scale must have N elements")
+    dev = weight_h.device
+    qweight = torch.empty((n, k // 2), dtype=torch.uint8, device=dev)
+    packed_scales = torch.empty((n, max(k // 64, 1)), dtype=torch.float16, device=dev)
+    channel_scales = torch.empty((n,), dtype=torch.float16, device=dev)
+    with _DeviceGuard(dev):
+        rc = lib.b200w4a4_pack_weight(
+            weight_h.data_ptr(), scale_h.data_ptr() if scale_h is not None else None,
+            qweight.data_ptr(), packed_scales.data_ptr(), channel_scales.data_ptr(), n, k,
+            _stream_ptr(dev))
+    _lib.check(rc, "pack_weight")
+    return qweight, packed_scales, channel_scales
+
+
+_PREPARED: dict = {}
+
+
+def _version_of(t: torch.Tensor) -> int:
+    try:
+        return t._version
+    except RuntimeError:  # inference tensors carry no version counter
+        return -1
+
+
+def prepare_b200_weight(qweight: torch.Tensor, wscales: torch.Tensor):
+    """Load-time repack of one layer: (vdm_weight_packed, vdm_weight_scale_packed) ->
+    (w_b200 u8 [N,K/2] in the TMA/tcgen05 staging layout, plain scale f16 [N]).  Cached."""
+    key = (qweight.data_ptr(), _version_of(qweight), tuple(qweight.shape), qweight.device.index,
+           wscales.data_ptr(), _version_of(wscales))
+    hit = _PREPARED.get(key)
+    if hit is not None:
+        return hit
+    lib = _load_ext()
+    _require_cuda(qweight, "qweight")
+    n, k2 = qweight.shape
+    k = 2 * k2
+    if qweight.dtype != torch.uint8 or wscales.dtype != torch.float16:
+        raise RuntimeError("qweight must be uint8 and wscales float16")
+    qw = qweight if qweight.is_contiguous() else qweight.contiguous()
+    ws = wscales if wscales.is_contiguous() else wscales.contiguous()
+    dev = qweight.device
+    w_b200 = torch.empty((n, k2), dtype=torch.uint8, device=dev)
+    w_scale = torch.empty((n,), dtype=torch.float16, device=dev)
+    with _DeviceGuard(dev):
+        rc = lib.b200w4a4_repack_weight(qw.data_ptr(), w_b200.data_ptr(), ws.data_ptr(),
+                                        w_scale.data_ptr(), n, k, _stream_ptr(dev))
+    _lib.check(rc, "repack_weight")
+    _PREPARED[key] = (w_b200, w_scale)
+    weakref.finalize(qweight, _PREPARED.pop, key, None)
+    return w_b200, w_scale
+
+
+# --------------------------------------------------------------------------- forward ops
+def _linear_prepared(x_2d: torch.Tensor, w_b200: torch.Tensor, w_scale: torch.Tensor,
+                     bias_h: Optional[torch.Tensor], clip_ratio: float) -> torch.Tensor:
+    lib = _load_ext()
+    m, k = x_2d.shape
+    n = w_b200.shape[0]
+    dev = x_2d.device
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    if m == 0:
+        return out
+    ws_bytes = lib.b200w4a4_linear_workspace_bytes(m, k)
+    workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+    with _DeviceGuard(dev):
+        rc = lib.b200w4a4_linear(
+            x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], w_b200.data_ptr(), w_scale.data_ptr(),
+            bias_h.data_ptr() if bias_h is not None else None, out.data_ptr(),
+            workspace.data_ptr(), ws_bytes, m, n, k, float(clip_ratio), _stream_ptr(dev))
+    _lib.check(rc, "linear")
+    return out
+
+
+def linear_vdm_w4a4(
+    x: torch.Tensor,
+    qweight: torch.Tensor,
+    wscales: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    clip_ratio: float = 1.0,
+    bias_half: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    _load_ext()
+    _require_cuda(x, "x")
+    x_2d, orig_shape = _as_2d_contiguous(x)
+    _check_linear_shapes(x_2d, qweight, wscales)
+    w_b200, w_scale = prepare_b200_weight(qweight, wscales)
+    b = bias_half if bias_half is not None else bias
+    if b is not None:
+        b = b.detach().reshape(-1)
+        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
+            b = b.half().contiguous().clone()
+        if b.numel() != qweight.shape[0]:
+            raise ValueError("bias must have N elements")
+    out = _linear_prepared(x_2d, w_b200, w_scale, b, clip_ratio)
+    return out.view(*orig_shape, -1)
+
+
+def quantize_activation_per_token(x: torch.Tensor, clip_ratio: float = 1.0):
+    """Returns (qact int8 [M,K], ascales fp32 [M], act_scales fp16 [M]).
+
+    `ascales` are the exact scales the GEMM uses; `act_scales` is their fp16 rounding, kept
+    for signature compatibility with the reference (which returns fp16 scales)."""
+    lib = _load_ext()
+    _require_cuda(x, "x")
+    x_2d, _ = _as_2d_contiguous(x)
+    m, k = x_2d.shape
+    if k % WARP_K != 0:
+        raise ValueError(f"K={k} must be a multiple of {WARP_K}")
+    dev = x_2d.device
+    qact = torch.empty((m, k), dtype=torch.int8, device=dev)
+    ascales = torch.empty((m,), dtype=torch.float32, device=dev)
+    if m > 0:
+        with _DeviceGuard(dev):
+            rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype],
+                                           qact.data_ptr(), QACT_INT8, ascales.data_ptr(), m, k,
+                                           float(clip_ratio), _stream_ptr(dev))
+        _lib.check(rc, "quantize_act")
+    return qact, ascales, ascales.half()
+
+
+def quantize_activation_nibbles(x: torch.Tensor, clip_ratio: float = 1.0):
+    """Same quantiser, packed container: (u8 [M,K/2] with code 2b in the low and 2b+1 in the
+    high nibble, fp32 scales [M])."""
+    lib = _load_ext()
+    _require_cuda(x, "x")
+    x_2d, _ = _as_2d_contiguous(x)
+    m, k = x_2d.shape
+    if k % WARP_K != 0:
+        raise ValueError(f"K={k} must be a multiple of {WARP_K}")
+    dev = x_2d.device
+    qact = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    ascales = torch.empty((m,), dtype=torch.float32, device=dev)
+    if m > 0:
+        with _DeviceGuard(dev):
+            rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype],
+                                           qact.data_ptr(), QACT_NIBBLE, ascales.data_ptr(), m, k,
+                                           float(clip_ratio), _stream_ptr(dev))
+        _lib.check(rc, "quantize_act")
+    return qact, ascales
+
+
+def linear_prequantized(qact: torch.Tensor, ascales: torch.Tensor, qweight: torch.Tensor,
+                        wscales: torch.Tensor, *, return_acc: bool = False):
+    """GEMM only, no bias: qact int8 [M,K] and fp32 ascales [M] as returned by
+    quantize_activation_per_token.  With return_acc=True also returns the int32 accumulators."""
+    lib = _load_ext()
+    _require_cuda(qact, "qact")
+    if qact.dtype != torch.int8 or ascales.dtype != torch.float32:
+        raise RuntimeError("qact must be int8 [M,K] and ascales float32 [M]")
+    qact = qact.contiguous()
+    ascales = ascales.contiguous()
+    _check_linear_shapes(qact, qweight, wscales)
+    w_b200, w_scale = prepare_b200_weight(qweight, wscales)
+    m, k = qact.shape
+    n = qweight.shape[0]
+    dev = qact.device
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    acc = torch.empty((m, n), dtype=torch.int32, device=dev) if return_acc else None
+    if m > 0:
+        with _DeviceGuard(dev):
+            rc = lib.b200w4a4_gemm(qact.data_ptr(), ascales.data_ptr(), w_b200.data_ptr(),
+                                   w_scale.data_ptr(), None, out.data_ptr(),
+                                   acc.data_ptr() if acc is not None else None, m, n, k,
+                                   _stream_ptr(dev))
+        _lib.check(rc, "gemm")
+    return (out, acc) if return_acc else out
+
+
+def linear_vdm_w4a4_qkv(
+    x: torch.Tensor,
+    q_weight_packed: torch.Tensor,
+    q_weight_scale: torch.Tensor,
+    k_weight_packed: torch.Tensor,
+    k_weight_scale: torch.Tensor,
+    v_weight_packed: torch.Tensor,
+    v_weight_scale: torch.Tensor,
+    q_bias: Optional[torch.Tensor] = None,
+    k_bias: Optional[torch.Tensor] = None,
+    v_bias: Optional[torch.Tensor] = None,
+    clip_ratio: float = 1.0,
+    w_qkv_packed: Optional[torch.Tensor] = None,
+    w_qkv_scale: Optional[torch.Tensor] = None,
+    qkv_bias_half: Optional[torch.Tensor] = None,
+):
+    """One activation quantisation and one GEMM with N = 3*D; returns three views split along
+    the last dimension.  Concatenating v1 buffers along dim 0 is valid because one 128-channel
+    block of the v1 layout is exactly 128 rows of the [N,K/2] view."""
+    if w_qkv_packed is None or w_qkv_scale is None:
+        w_qkv_packed = torch.cat([q_weight_packed, k_weight_packed, v_weight_packed], dim=0).contiguous()
+        w_qkv_scale = torch.cat([q_weight_scale, k_weight_scale, v_weight_scale], dim=0).contiguous()
+    n = q_weight_packed.shape[0]
+    if qkv_bias_half is None and (q_bias is not None or k_bias is not None or v_bias is not None):
+        device = w_qkv_packed.device
+
+        def _b(b):
+            return b.half().contiguous() if b is not None else torch.zeros(n, dtype=torch.float16, device=device)
+
+        qkv_bias_half = torch.cat([_b(q_bias), _b(k_bias), _b(v_bias)], dim=0)
+    qkv = linear_vdm_w4a4(x, w_qkv_packed, w_qkv_scale, bias=None, clip_ratio=clip_ratio,
+                          bias_half=qkv_bias_half)
+    return qkv.split(n, dim=-1)
+
+
+# --------------------------------------------------------------------------- test / debug helpers
+def unpack_codes(packed: torch.Tensor, rows: int, k: int, which: int) -> torch.Tensor:
+    """int8 codes [rows,k] of a packed buffer: which = 1 repacked weight, 2 v1 weight, 3 nibble rows."""
+    lib = _load_ext()
+    _require_cuda(packed, "packed")
+    codes = torch.empty((rows, k), dtype=torch.int8, device=packed.device)
+    with _DeviceGuard(packed.device):
+        rc = lib.b200w4a4_unpack_codes(packed.contiguous().data_ptr(), codes.data_ptr(), rows, k,
+                                       which, _stream_ptr(packed.device))
+    _lib.check(rc, "unpack_codes")
+    return codes
+
+
+def set_cta_group(cta_group: int) -> int:
+    """Selects the GEMM variant (1: one CTA per 128x256 tile, 2: CTA pair per 256x256 tile)."""
+    rc = _load_ext().b200w4a4_set_cta_group(int(cta_group))
+    if rc < 0:
+        _lib.check(rc, "set_cta_group")
+    return rc
+
+
+def last_device_status(device: Optional[int] = None) -> int:
+    """Synchronises the device and returns (and clears) the kernels' time-out status word."""
+    idx = torch.cuda.current_device() if device is None else int(device)
+    return _load_ext().b200w4a4_last_device_status(idx)

@@ -1,0 +1,136 @@
+/*
+ * b200w4a4 -- C ABI of the sm_100a W4A4 linear-layer library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t; NULL = legacy default stream),
+ * launches asynchronously on that stream, allocates nothing, and returns
+ * 0 on success or a negative B200W4A4_E* code.  The caller owns all buffers.
+ * Shape constraints kept from the reference extension
+ * (vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu:769-789): K % 64 == 0,
+ * N % 128 == 0, M >= 1 arbitrary (no padding to 256 rows is needed).
+ *
+ * Each declaration cites the reference interface it stands in for
+ * (paths relative to the DSAQuant repository root).
+ */
+#ifndef B200W4A4_H_
+#define B200W4A4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200W4A4_ABI_VERSION 1
+
+/* error codes */
+#define B200W4A4_OK 0
+#define B200W4A4_EINVAL (-1)      /* null pointer, bad size, bad enum */
+#define B200W4A4_ESHAPE (-2)      /* K % 64 != 0, N % 128 != 0, M < 1, ... */
+#define B200W4A4_EALIGN (-3)      /* pointer not 16-byte aligned */
+#define B200W4A4_EARCH (-4)       /* device is not compute capability 10.0 */
+#define B200W4A4_ECUDA (-5)       /* CUDA runtime / driver call failed */
+#define B200W4A4_EWORKSPACE (-6)  /* workspace too small */
+#define B200W4A4_EDEVICE (-7)     /* a kernel recorded a device-side time-out */
+
+/* activation dtypes accepted by the quantiser */
+#define B200W4A4_F16 0
+#define B200W4A4_BF16 1
+#define B200W4A4_F32 2
+
+/* containers for activation codes */
+#define B200W4A4_QACT_INT8 0    /* int8 [M,K], one code per byte (GEMM input) */
+#define B200W4A4_QACT_NIBBLE 1  /* u8 [M,K/2], code 2b low nibble, 2b+1 high nibble */
+
+/* `which` of b200w4a4_unpack_codes */
+#define B200W4A4_CODES_WEIGHT_B200 1  /* repacked weight  -> int8 [N,K] */
+#define B200W4A4_CODES_WEIGHT_V1 2    /* vdm_weight_packed -> int8 [N,K] */
+#define B200W4A4_CODES_ACT_NIBBLE 3   /* nibble activations -> int8 [M,K] */
+
+/* ABI version of the loaded library (compare with B200W4A4_ABI_VERSION). */
+int b200w4a4_version(void);
+
+/* Human-readable text for an error code.  Never NULL. */
+const char* b200w4a4_strerror(int code);
+
+/* Device properties; returns B200W4A4_EARCH unless the device is 10.0.
+ * Stands in for the JIT arch selection of vdm_infer/kernels/vdm_w4a4.py:42-69,
+ * which gains the sm_100a target. */
+int b200w4a4_query(int device, int* sm_count, int* cc_major, int* cc_minor);
+
+/* ---- weights (load / export time) --------------------------------------- */
+
+/* fp16 weight [N,K] + per-channel fp16 scale [N] -> the three buffers of the
+ * vdm_w4a4_packed_v1 format: vdm_packed u8 [N,K/2], vdm_scale_packed f16 [N,K/64],
+ * vdm_scale f16 [N].  Replaces ext.pack_weight_with_scale
+ * (vdm_w4a4_kernel.cu:697-728; python vdm_w4a4.py:209-214).
+ * If ch_scale is NULL the scale is computed as absmax/7 per channel into
+ * vdm_scale first: ext.quantize_weight_per_channel (vdm_w4a4_kernel.cu:730-763;
+ * vdm_w4a4.py:217-219). */
+int b200w4a4_pack_weight(const void* w_f16, const void* ch_scale_f16, void* vdm_packed,
+                         void* vdm_scale_packed, void* vdm_scale, int N, int K, void* stream);
+
+/* Bytes of the tcgen05-friendly weight buffer for an [N,K] layer. */
+size_t b200w4a4_repack_bytes(int N, int K);
+
+/* Load-time repack: vdm_weight_packed (v1 fragment order) -> row-major nibble
+ * layout staged by TMA; optionally vdm_weight_scale_packed [N,K/64] -> plain
+ * per-channel scale [N] (pass NULLs to skip).  Hooks in where
+ * load_packed_quantized_model registers the buffers
+ * (vdm_infer/checkpoints/packed_checkpoint.py:52-148). */
+int b200w4a4_repack_weight(const void* vdm_packed, void* w_b200, const void* vdm_scale_packed,
+                           void* w_scale_plain, int N, int K, void* stream);
+
+/* ---- activations -------------------------------------------------------- */
+
+/* Bytes of the code buffer for M x K activations in the given container. */
+size_t b200w4a4_qact_bytes(int M, int K, int container);
+
+/* Dynamic per-token int4 quantise: x [M,K] row-major (ld = K) of dtype
+ * x_dtype -> codes in `container`, fp32 scale [M].
+ * scale = (max(absmax,1e-5)/7)*clip, code = clamp(rint(x/scale),-8,7).
+ * Replaces token_scale_kernel + act_quantize_per_token_kernel
+ * (vdm_w4a4_kernel.cu:459-516) / ext.quantize_activation_per_token (:840-873). */
+int b200w4a4_quantize_act(const void* x, int x_dtype, void* qact, int container, float* act_scale,
+                          int M, int K, float clip, void* stream);
+
+/* ---- GEMM --------------------------------------------------------------- */
+
+/* out[m,n] = fp16( float(sum_k qa[m,k]*qw[n,k]) * (act_scale[m]*w_scale[n]) + bias[n] )
+ * qact: int8 container [M,K]; w_b200: repacked weight; w_scale f16 [N];
+ * bias f16 [N] or NULL; out f16 [M,N] (ld = N); acc_dump int32 [M,N] or NULL
+ * (exact accumulators, for tests).  Replaces linear_w4a4_kernel
+ * (vdm_w4a4_kernel.cu:627-686) / ext.linear_prequantized (:876-918). */
+int b200w4a4_gemm(const void* qact, const float* act_scale, const void* w_b200, const void* w_scale,
+                  const void* bias, void* out, int32_t* acc_dump, int M, int N, int K,
+                  void* stream);
+
+/* Workspace bytes b200w4a4_linear needs for an M x K activation. */
+size_t b200w4a4_linear_workspace_bytes(int M, int K);
+
+/* Quantise + GEMM: what QuantLinear.forward and the fused QKV projection call.
+ * Replaces ext.linear_dynamic / ext.linear_dynamic_bias
+ * (vdm_w4a4_kernel.cu:765-838; python linear_vdm_w4a4, vdm_w4a4.py:222-244). */
+int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* w_scale,
+                    const void* bias, void* out, void* workspace, size_t workspace_bytes, int M,
+                    int N, int K, float clip, void* stream);
+
+/* ---- helpers ------------------------------------------------------------ */
+
+/* Extract int8 codes [rows,K] from a packed buffer (parity tests). */
+int b200w4a4_unpack_codes(const void* packed, int8_t* codes, int rows, int K, int which,
+                          void* stream);
+
+/* Select the GEMM variant: 1 = one CTA per 128x256 tile, 2 = CTA pair per
+ * 256x256 tile (cta_group::2).  Returns the previous value, or EINVAL. */
+int b200w4a4_set_cta_group(int cta_group);
+
+/* Synchronises `device`, returns and clears its device status word:
+ * 0, or the code (> 0) of the kernel role whose bounded wait ran out. */
+int b200w4a4_last_device_status(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200W4A4_H_ */
