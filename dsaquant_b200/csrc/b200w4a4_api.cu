@@ -95,7 +95,7 @@ int current_cta_group() {
   int g = g_cta_group.load(std::memory_order_relaxed);
   if (g == 0) {
     const char* e = getenv("B200W4A4_CTA_GROUP");
-    g = (e != nullptr && e[0] == '2') ? 2 : 1;
+    g = (e != nullptr && e[0] == '1') ? 1 : 2;  // the CTA-pair kernel is the default
     g_cta_group.store(g, std::memory_order_relaxed);
   }
   return g;

@@ -4,12 +4,12 @@
 // (vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu:627-686, mma.sync m16n8k64 s4 fed
 // from registers) with a persistent, warp-specialised tcgen05 kernel:
 //
-//   warp 0      TMA producer: activation codes (int8 container, K-major, 128B
-//               swizzle) and packed int4 weight tiles (two codes per byte)
+//   warp 0      TMA producer: activation codes (int8 container, K-major, 128B swizzle)
 //   warp 1      owns TMEM; one lane issues tcgen05.mma kind::i8 (K=32 slices)
-//   warps 2-5   unpack the int4 weight tile into the int8 K-major/128B-swizzle
+//   warp 2      TMA producer: packed int4 weight tiles (two codes per byte)
+//   warps 3-6   unpack the int4 weight tile into the int8 K-major/128B-swizzle
 //               tile the tensor core reads (tcgen05 has no s4 kind)
-//   warps 6-9   epilogue: tcgen05.ld the int32 accumulator, dequantise with the
+//   warps 7-10  epilogue: tcgen05.ld the int32 accumulator, dequantise with the
 //               per-token x per-channel scales, add bias, fp16, TMA store
 //
 // Weight nibble convention (produced by the load-time repack, see
@@ -51,21 +51,28 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK;        // int8
   static constexpr int BP_BYTES = B_ROWS * BK / 2;
   static constexpr int BU_BYTES = B_ROWS * BK;
-  static constexpr int S1 = (CG == 1) ? 3 : 4;   // TMA ring depth (A + packed B)
-  static constexpr int S2 = (CG == 1) ? 2 : 3;   // unpacked-B ring depth
-  static constexpr int STAGE1 = A_BYTES + BP_BYTES;
-  static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16, per warp, double buffered
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF;
-  static constexpr int OFF_RING1 = 0;
-  static constexpr int OFF_RING2 = OFF_RING1 + S1 * STAGE1;
-  static constexpr int OFF_EPI = OFF_RING2 + S2 * BU_BYTES;
+  // Three independent rings.  A tiles (int8, TMA) and unpacked weight tiles are released by
+  // the MMA's commit; packed weight tiles are released as soon as they have been unpacked, so
+  // that ring can be shallower for the same prefetch distance.
+  static constexpr int SA = (CG == 1) ? 4 : 7;   // A ring depth
+  static constexpr int SB = (CG == 1) ? 3 : 4;   // packed-B ring depth
+  static constexpr int SU = (CG == 1) ? 3 : 4;   // unpacked-B ring depth
+  static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16 per epilogue warp
+  static constexpr int EPI_BYTES = 4 * EPI_BUF;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_BP = OFF_A + SA * A_BYTES;
+  static constexpr int OFF_BU = OFF_BP + SB * BP_BYTES;
+  static constexpr int OFF_EPI = OFF_BU + SU * BU_BYTES;
   static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
-  static constexpr int NUM_BARS = 3 * S1 + 2 * S2 + 4 + 1;
+  static constexpr int NUM_BARS = 2 * SA + 2 * SB + 2 * SU + 4 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + 8 * NUM_BARS + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1024 B
-  static constexpr int THREADS = 320;
+  static constexpr int WARP_A_PRODUCER = 0, WARP_MMA = 1, WARP_B_PRODUCER = 2;
+  static constexpr int WARP_UNPACK0 = 3, WARP_EPI0 = 7;
+  static constexpr int THREADS = 352;            // 11 warps
   static constexpr int TMEM_COLS = 512;          // two 128 x 256 int32 accumulators
-  static_assert(STAGE1 % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
+  static constexpr int GROUP_M = 8;              // tile rasterisation: walk 8 row-tiles per column-tile
+  static_assert(BP_BYTES % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
 
@@ -157,6 +164,21 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
 
 }  // namespace detail
 
+// Tile index -> (row tile, column tile).  Consecutive indices walk GROUP_M row tiles of one
+// column tile before moving to the next column tile, so the CTAs that run at the same time share
+// both their activation rows and their weight rows through L2 instead of all fetching one of them.
+template <int CG>
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  constexpr int G = GemmCfg<CG>::GROUP_M;
+  const int per_group = G * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * G;
+  const int rows = (m_tiles - first_m < G) ? (m_tiles - first_m) : G;
+  const int in_group = tile - group * per_group;
+  mt = first_m + in_group % rows;
+  nt = in_group / rows;
+}
+
 template <int CG>
 __global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -174,26 +196,30 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   // ---- barrier map ---------------------------------------------------------
   const uint32_t bar0 = smem_base + C::OFF_BAR;
-  auto bar_tma_full = [&](int s) { return bar0 + 8u * s; };                       // A (+Bp when CG==1)
-  auto bar_bp_full = [&](int s) { return bar0 + 8u * (C::S1 + s); };              // packed B (CG==2)
-  auto bar_ring1_free = [&](int s) { return bar0 + 8u * (2 * C::S1 + s); };       // MMA + unpackers done
-  auto bar_bu_full = [&](int s) { return bar0 + 8u * (3 * C::S1 + s); };
-  auto bar_bu_free = [&](int s) { return bar0 + 8u * (3 * C::S1 + C::S2 + s); };
-  auto bar_acc_full = [&](int b) { return bar0 + 8u * (3 * C::S1 + 2 * C::S2 + b); };
-  auto bar_acc_free = [&](int b) { return bar0 + 8u * (3 * C::S1 + 2 * C::S2 + 2 + b); };
+  auto bar_a_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_a_free = [&](int s) { return bar0 + 8u * (C::SA + s); };
+  auto bar_bp_full = [&](int s) { return bar0 + 8u * (2 * C::SA + s); };
+  auto bar_bp_free = [&](int s) { return bar0 + 8u * (2 * C::SA + C::SB + s); };
+  auto bar_bu_full = [&](int s) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + s); };
+  auto bar_bu_free = [&](int s) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + C::SU + s); };
+  auto bar_acc_full = [&](int b) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + 2 * C::SU + b); };
+  auto bar_acc_free = [&](int b) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + 2 * C::SU + 2 + b); };
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_gen + C::OFF_BAR + 8 * (C::NUM_BARS - 1));
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::S1; ++s) {
-      ptx::mbar_init(bar_tma_full(s), 1);
-      ptx::mbar_init(bar_bp_full(s), 1);
-      ptx::mbar_init(bar_ring1_free(s), 1 + 4);   // one MMA commit + four unpack warps
+    for (int s = 0; s < C::SA; ++s) {
+      ptx::mbar_init(bar_a_full(s), 1);
+      ptx::mbar_init(bar_a_free(s), 1);           // one MMA commit
     }
-    for (int s = 0; s < C::S2; ++s) {
+    for (int s = 0; s < C::SB; ++s) {
+      ptx::mbar_init(bar_bp_full(s), 1);
+      ptx::mbar_init(bar_bp_free(s), 4);          // four unpack warps
+    }
+    for (int s = 0; s < C::SU; ++s) {
       ptx::mbar_init(bar_bu_full(s), 4 * CG);     // unpack warps of every CTA in the group
-      ptx::mbar_init(bar_bu_free(s), 1);
+      ptx::mbar_init(bar_bu_free(s), 1);          // one MMA commit
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_acc_full(b), 1);
@@ -202,12 +228,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == C::WARP_A_PRODUCER && lane == 0) {
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_out);
   }
-  if (warp == 1) {
+  if (warp == C::WARP_MMA) {
     ptx::tmem_alloc<CG>(ptx::smem_u32(tmem_holder), C::TMEM_COLS);
     ptx::tmem_relinquish<CG>();
   }
@@ -223,35 +249,31 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int tile_step = static_cast<int>(gridDim.x) / CG;
   const int kblocks = (p.K + C::BK - 1) / C::BK;
 
-  if (warp == 0) {
-    // ===================== TMA producer =====================
+  if (warp == C::WARP_A_PRODUCER) {
+    // ===================== TMA producer: activation codes =====================
     if (lane == 0) {
+      // Both CTAs of a pair feed the leader's MMA: byte counts go to the leader's barrier.
       uint32_t it = 0;
       bool alive = true;
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
-        const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+        int mt, nt;
+        tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
         const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM;
-        const int n0 = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % C::S1;
-          const uint32_t ph = (it / C::S1) & 1;
-          if (!detail::wait_bar<CG == 2>(bar_ring1_free(s), ph ^ 1, abort_flag, p.status,
+          const int s = it % C::SA;
+          const uint32_t ph = (it / C::SA) & 1;
+          if (!detail::wait_bar<CG == 2>(bar_a_free(s), ph ^ 1, abort_flag, p.status,
                                          DEV_TIMEOUT_PRODUCER)) {
             alive = false;
             break;
           }
-          const uint32_t a_dst = smem_base + C::OFF_RING1 + s * C::STAGE1;
-          const uint32_t bp_dst = a_dst + C::A_BYTES;
+          const uint32_t dst = smem_base + C::OFF_A + s * C::A_BYTES;
           if constexpr (CG == 1) {
-            ptx::mbar_arrive_expect_tx(bar_tma_full(s), C::A_BYTES + C::BP_BYTES);
-            ptx::tma_load_2d(a_dst, &tm_a, bar_tma_full(s), kb * C::BK, m0);
-            ptx::tma_load_2d(bp_dst, &tm_w, bar_tma_full(s), kb * (C::BK / 2), n0);
+            ptx::mbar_arrive_expect_tx(bar_a_full(s), C::A_BYTES);
+            ptx::tma_load_2d(dst, &tm_a, bar_a_full(s), kb * C::BK, m0);
           } else {
-            // A halves of both CTAs are consumed by the leader's MMA: credit the leader's barrier.
-            if (leader) ptx::mbar_arrive_expect_tx(bar_tma_full(s), 2 * C::A_BYTES);
-            ptx::tma_load_2d_pair(a_dst, &tm_a, ptx::mapa(bar_tma_full(s), 0), kb * C::BK, m0);
-            ptx::mbar_arrive_expect_tx(bar_bp_full(s), C::BP_BYTES);
-            ptx::tma_load_2d(bp_dst, &tm_w, bar_bp_full(s), kb * (C::BK / 2), n0);
+            if (leader) ptx::mbar_arrive_expect_tx(bar_a_full(s), 2 * C::A_BYTES);
+            ptx::tma_load_2d_pair(dst, &tm_a, ptx::mapa(bar_a_full(s), 0), kb * C::BK, m0);
           }
         }
       }
@@ -262,7 +284,35 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == C::WARP_B_PRODUCER) {
+    // ===================== TMA producer: packed int4 weights =====================
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
+        int mt, nt;
+        tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
+        const int n0 = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::SB;
+          const uint32_t ph = (it / C::SB) & 1;
+          if (!detail::wait_bar<false>(bar_bp_free(s), ph ^ 1, abort_flag, p.status,
+                                       DEV_TIMEOUT_PRODUCER)) {
+            alive = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(bar_bp_full(s), C::BP_BYTES);
+          ptx::tma_load_2d(smem_base + C::OFF_BP + s * C::BP_BYTES, &tm_w, bar_bp_full(s),
+                           kb * (C::BK / 2), n0);
+        }
+      }
+      if (!alive) {
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == C::WARP_MMA) {
     // ===================== MMA issuer =====================
     if (lane == 0 && (CG == 1 || leader)) {
       constexpr uint32_t idesc = make_i8_idesc(C::BM * CG, C::BN);
@@ -280,20 +330,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + ab * C::BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s1 = it % C::S1, s2 = it % C::S2;
-          const uint32_t ph1 = (it / C::S1) & 1, ph2 = (it / C::S2) & 1;
-          if (!detail::wait_bar<CG == 2>(bar_tma_full(s1), ph1, abort_flag, p.status,
+          const int sa = it % C::SA, su = it % C::SU;
+          const uint32_t pha = (it / C::SA) & 1, phu = (it / C::SU) & 1;
+          if (!detail::wait_bar<CG == 2>(bar_a_full(sa), pha, abort_flag, p.status,
                                          DEV_TIMEOUT_MMA) ||
-              !detail::wait_bar<CG == 2>(bar_bu_full(s2), ph2, abort_flag, p.status,
+              !detail::wait_bar<CG == 2>(bar_bu_full(su), phu, abort_flag, p.status,
                                          DEV_TIMEOUT_MMA)) {
             alive = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint64_t adesc =
-              make_kmajor_sw128_desc(smem_base + C::OFF_RING1 + s1 * C::STAGE1);
-          const uint64_t bdesc =
-              make_kmajor_sw128_desc(smem_base + C::OFF_RING2 + s2 * C::BU_BYTES);
+          const uint64_t adesc = make_kmajor_sw128_desc(smem_base + C::OFF_A + sa * C::A_BYTES);
+          const uint64_t bdesc = make_kmajor_sw128_desc(smem_base + C::OFF_BU + su * C::BU_BYTES);
 #pragma unroll
           for (int k = 0; k < C::BK / 32; ++k) {
             // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
@@ -301,11 +349,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                (kb > 0 || k > 0) ? 1u : 0u);
           }
           if constexpr (CG == 1) {
-            ptx::mma_commit(bar_ring1_free(s1));
-            ptx::mma_commit(bar_bu_free(s2));
+            ptx::mma_commit(bar_a_free(sa));
+            ptx::mma_commit(bar_bu_free(su));
           } else {
-            ptx::mma_commit_pair(bar_ring1_free(s1), 0x3);
-            ptx::mma_commit_pair(bar_bu_free(s2), 0x3);
+            ptx::mma_commit_pair(bar_a_free(sa), 0x3);
+            ptx::mma_commit_pair(bar_bu_free(su), 0x3);
           }
         }
         if (alive) {
@@ -316,9 +364,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < C::WARP_EPI0) {
     // ===================== int4 -> int8 weight unpack =====================
-    const int tid_u = static_cast<int>(threadIdx.x) - 64;  // 0..127
+    const int tid_u = static_cast<int>(threadIdx.x) - 32 * C::WARP_UNPACK0;  // 0..127
     const uint32_t row_x = static_cast<uint32_t>((tid_u >> 2) & 7);
     const uint32_t c2 = static_cast<uint32_t>(tid_u & 3) * 2;
     const uint32_t hi_off = ((c2 ^ row_x) << 4);
@@ -327,17 +375,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     bool alive = true;
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int s1 = it % C::S1, s2 = it % C::S2;
-        const uint32_t ph1 = (it / C::S1) & 1, ph2 = (it / C::S2) & 1;
-        const uint32_t full_bar = (CG == 1) ? bar_tma_full(s1) : bar_bp_full(s1);
-        if (!detail::wait_bar<false>(full_bar, ph1, abort_flag, p.status, DEV_TIMEOUT_UNPACK) ||
-            !detail::wait_bar<CG == 2>(bar_bu_free(s2), ph2 ^ 1, abort_flag, p.status,
+        const int sb = it % C::SB, su = it % C::SU;
+        const uint32_t phb = (it / C::SB) & 1, phu = (it / C::SU) & 1;
+        if (!detail::wait_bar<false>(bar_bp_full(sb), phb, abort_flag, p.status,
+                                     DEV_TIMEOUT_UNPACK) ||
+            !detail::wait_bar<CG == 2>(bar_bu_free(su), phu ^ 1, abort_flag, p.status,
                                        DEV_TIMEOUT_UNPACK)) {
           alive = false;
           break;
         }
-        const uint32_t bp = smem_base + C::OFF_RING1 + s1 * C::STAGE1 + C::A_BYTES;
-        const uint32_t bu = smem_base + C::OFF_RING2 + s2 * C::BU_BYTES;
+        const uint32_t bp = smem_base + C::OFF_BP + sb * C::BP_BYTES;
+        const uint32_t bu = smem_base + C::OFF_BU + su * C::BU_BYTES;
 #pragma unroll
         for (int j = 0; j < C::B_ROWS * 4 / 128; ++j) {
           const int q = tid_u + 128 * j;          // 16-byte packed chunk index in the tile
@@ -355,24 +403,25 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::mbar_arrive(bar_ring1_free(s1));
+          ptx::mbar_arrive(bar_bp_free(sb));
           if constexpr (CG == 1)
-            ptx::mbar_arrive(bar_bu_full(s2));
+            ptx::mbar_arrive(bar_bu_full(su));
           else
-            ptx::mbar_arrive_cluster(bar_bu_full(s2), 0);
+            ptx::mbar_arrive_cluster(bar_bu_full(su), 0);
         }
       }
     }
   } else {
     // ===================== epilogue =====================
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-    const uint32_t stage_base = smem_base + C::OFF_EPI + (warp - 6) * 2 * C::EPI_BUF;
+    const uint32_t stage_buf = smem_base + C::OFF_EPI + (warp - C::WARP_EPI0) * C::EPI_BUF;
+    const uint32_t stage = stage_buf + 128u * lane;
     const uint32_t row_sw = static_cast<uint32_t>(lane & 7);
     uint32_t local_tile = 0;
-    uint32_t store_it = 0;
     bool alive = true;
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
-      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      int mt, nt;
+      tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
       const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM + quad * 32;
       const int n0 = nt * C::BN;
       const uint32_t ab = local_tile & 1;
@@ -405,11 +454,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int col0 = n0 + 32 * c;
         const bool cols_valid = col0 < p.N;  // N is a multiple of 128: a 32-chunk is all in or all out
         if ((c & 1) == 0) {
-          // Staging buffer reuse: the TMA store issued two groups ago must have read it.
-          if (lane == 0) ptx::tma_store_wait_read<1>();
+          // The previous TMA store must have finished reading the staging buffer.
+          if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();
         }
-        const uint32_t stage = stage_base + (store_it & 1) * C::EPI_BUF + 128u * lane;
         if (cols_valid) {
           if (p.acc_dump != nullptr && row < p.M) {
             int4* dst = reinterpret_cast<int4*>(p.acc_dump + static_cast<size_t>(row) * p.N + col0);
@@ -453,11 +501,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (col0 - 32 < p.N && m0 < p.M)
-              ptx::tma_store_2d(&tm_out, stage_base + (store_it & 1) * C::EPI_BUF, col0 - 32, m0);
+            if (col0 - 32 < p.N && m0 < p.M) ptx::tma_store_2d(&tm_out, stage_buf, col0 - 32, m0);
             ptx::tma_store_commit();
           }
-          ++store_it;
         }
       }
     }
@@ -468,7 +514,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   ptx::tc_fence_before_sync();
   __syncthreads();
   if constexpr (CG == 2) detail::cluster_sync_all();
-  if (warp == 1) {
+  if (warp == C::WARP_MMA) {
     __syncwarp();
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
