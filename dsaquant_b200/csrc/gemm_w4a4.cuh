@@ -4,13 +4,13 @@
 // (vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu:627-686, mma.sync m16n8k64 s4 fed
 // from registers) with a persistent, warp-specialised tcgen05 kernel:
 //
-//   warp 0      TMA producer: activation codes (int8 container, K-major, 128B swizzle)
-//   warp 1      owns TMEM; one lane issues tcgen05.mma kind::i8 (K=32 slices)
-//   warp 2      TMA producer: packed int4 weight tiles (two codes per byte)
-//   warps 3-6   unpack the int4 weight tile into the int8 K-major/128B-swizzle
-//               tile the tensor core reads (tcgen05 has no s4 kind)
-//   warps 7-10  epilogue: tcgen05.ld the int32 accumulator, dequantise with the
-//               per-token x per-channel scales, add bias, fp16, TMA store
+//   warp 0       TMA producer: activation codes (int8 container, K-major, 128B swizzle)
+//   warp 1       owns TMEM; one lane issues tcgen05.mma kind::i8 (K=32 slices)
+//   warp 2       TMA producer: packed int4 weight tiles (two codes per byte)
+//   warps 3-10   unpack the int4 weight tile into the int8 K-major/128B-swizzle
+//                tile the tensor core reads (tcgen05 has no s4 kind)
+//   warps 11-14  epilogue: tcgen05.ld the int32 accumulator, dequantise with the
+//                per-token x per-channel scales, add bias, fp16, TMA store
 //
 // Weight nibble convention (produced by the load-time repack, see
 // weight_pack.cuh): inside each 128-wide K block, byte (16*c + i) of a row
@@ -51,28 +51,29 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK;        // int8
   static constexpr int BP_BYTES = B_ROWS * BK / 2;
   static constexpr int BU_BYTES = B_ROWS * BK;
-  // Three independent rings.  A tiles (int8, TMA) and unpacked weight tiles are released by
-  // the MMA's commit; packed weight tiles are released as soon as they have been unpacked, so
-  // that ring can be shallower for the same prefetch distance.
-  static constexpr int SA = (CG == 1) ? 4 : 7;   // A ring depth
-  static constexpr int SB = (CG == 1) ? 3 : 4;   // packed-B ring depth
-  static constexpr int SU = (CG == 1) ? 3 : 4;   // unpacked-B ring depth
+  // Main ring: one stage = an A tile (TMA) + an unpacked weight tile; released by one MMA commit.
+  // Packed weight tiles live in a second, shallower ring that is released as soon as they have
+  // been unpacked.
+  static constexpr int S = (CG == 1) ? 3 : 5;
+  static constexpr int SB = (CG == 1) ? 3 : 4;
+  static constexpr int STAGE_BYTES = A_BYTES + BU_BYTES;
   static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16 per epilogue warp
   static constexpr int EPI_BYTES = 4 * EPI_BUF;
-  static constexpr int OFF_A = 0;
-  static constexpr int OFF_BP = OFF_A + SA * A_BYTES;
-  static constexpr int OFF_BU = OFF_BP + SB * BP_BYTES;
-  static constexpr int OFF_EPI = OFF_BU + SU * BU_BYTES;
+  static constexpr int OFF_MAIN = 0;
+  static constexpr int OFF_BP = OFF_MAIN + S * STAGE_BYTES;
+  static constexpr int OFF_EPI = OFF_BP + SB * BP_BYTES;
   static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
-  static constexpr int NUM_BARS = 2 * SA + 2 * SB + 2 * SU + 4 + 1;
+  static constexpr int NUM_BARS = 2 * S + 2 * SB + 4 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + 8 * NUM_BARS + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1024 B
   static constexpr int WARP_A_PRODUCER = 0, WARP_MMA = 1, WARP_B_PRODUCER = 2;
-  static constexpr int WARP_UNPACK0 = 3, WARP_EPI0 = 7;
-  static constexpr int THREADS = 352;            // 11 warps
+  static constexpr int WARP_UNPACK0 = 3, UNPACK_WARPS = 8, WARP_EPI0 = WARP_UNPACK0 + UNPACK_WARPS;
+  static constexpr int UNPACK_THREADS = 32 * UNPACK_WARPS;
+  static constexpr int THREADS = 32 * (WARP_EPI0 + 4);
   static constexpr int TMEM_COLS = 512;          // two 128 x 256 int32 accumulators
   static constexpr int GROUP_M = 8;              // tile rasterisation: walk 8 row-tiles per column-tile
   static_assert(BP_BYTES % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
+  static_assert((B_ROWS * 4) % UNPACK_THREADS == 0, "unpack work split");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
 
@@ -113,14 +114,13 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 // Bounded wait on an mbarrier phase.  On time-out records `code` once, raises
 // the CTA-local abort flag and returns false; every other role sees the flag
 // (or the global status word) in its own wait and drains too.
-template <bool CLUSTER>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                          int* status, int code) {
+  if (ptx::mbar_probe(bar, parity)) return true;
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (true) {
-    bool ok = CLUSTER ? ptx::mbar_test_cluster(bar, parity) : ptx::mbar_test(bar, parity);
-    if (ok) return true;
+    if (ptx::mbar_test(bar, parity)) return true;
     if ((++spins & 0x3FF) == 0) {
       if (*abort_flag) return false;
       if (*reinterpret_cast<volatile int*>(status) != 0) {
@@ -179,6 +179,18 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   nt = in_group / rows;
 }
 
+// Ring cursor: slot index and phase parity, advanced without division.
+template <int DEPTH>
+struct RingPos {
+  uint32_t slot = 0, phase = 0;
+  __device__ __forceinline__ void advance() {
+    if (++slot == DEPTH) {
+      slot = 0;
+      phase ^= 1;
+    }
+  }
+};
+
 template <int CG>
 __global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -195,31 +207,28 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const bool leader = (cta_rank == 0);
 
   // ---- barrier map ---------------------------------------------------------
+  // full[s]      A bytes landed (TMA transaction count) AND every unpack warp of the group has
+  //              written its part of the int8 weight tile: the one barrier the MMA waits on.
+  // consumed[s]  the MMAs that read stage s have completed (tcgen05.commit): frees A and Bu.
   const uint32_t bar0 = smem_base + C::OFF_BAR;
-  auto bar_a_full = [&](int s) { return bar0 + 8u * s; };
-  auto bar_a_free = [&](int s) { return bar0 + 8u * (C::SA + s); };
-  auto bar_bp_full = [&](int s) { return bar0 + 8u * (2 * C::SA + s); };
-  auto bar_bp_free = [&](int s) { return bar0 + 8u * (2 * C::SA + C::SB + s); };
-  auto bar_bu_full = [&](int s) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + s); };
-  auto bar_bu_free = [&](int s) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + C::SU + s); };
-  auto bar_acc_full = [&](int b) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + 2 * C::SU + b); };
-  auto bar_acc_free = [&](int b) { return bar0 + 8u * (2 * C::SA + 2 * C::SB + 2 * C::SU + 2 + b); };
+  auto bar_full = [&](uint32_t s) { return bar0 + 8u * s; };
+  auto bar_consumed = [&](uint32_t s) { return bar0 + 8u * (C::S + s); };
+  auto bar_bp_full = [&](uint32_t s) { return bar0 + 8u * (2 * C::S + s); };
+  auto bar_bp_free = [&](uint32_t s) { return bar0 + 8u * (2 * C::S + C::SB + s); };
+  auto bar_acc_full = [&](uint32_t b) { return bar0 + 8u * (2 * C::S + 2 * C::SB + b); };
+  auto bar_acc_free = [&](uint32_t b) { return bar0 + 8u * (2 * C::S + 2 * C::SB + 2 + b); };
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_gen + C::OFF_BAR + 8 * (C::NUM_BARS - 1));
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::SA; ++s) {
-      ptx::mbar_init(bar_a_full(s), 1);
-      ptx::mbar_init(bar_a_free(s), 1);           // one MMA commit
+    for (int s = 0; s < C::S; ++s) {
+      ptx::mbar_init(bar_full(s), C::UNPACK_WARPS * CG + 1);  // unpack warps + the A producer
+      ptx::mbar_init(bar_consumed(s), 1);                     // one MMA commit
     }
     for (int s = 0; s < C::SB; ++s) {
       ptx::mbar_init(bar_bp_full(s), 1);
-      ptx::mbar_init(bar_bp_free(s), 4);          // four unpack warps
-    }
-    for (int s = 0; s < C::SU; ++s) {
-      ptx::mbar_init(bar_bu_full(s), 4 * CG);     // unpack warps of every CTA in the group
-      ptx::mbar_init(bar_bu_free(s), 1);          // one MMA commit
+      ptx::mbar_init(bar_bp_free(s), C::UNPACK_WARPS);
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_acc_full(b), 1);
@@ -252,29 +261,34 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == C::WARP_A_PRODUCER) {
     // ===================== TMA producer: activation codes =====================
     if (lane == 0) {
-      // Both CTAs of a pair feed the leader's MMA: byte counts go to the leader's barrier.
-      uint32_t it = 0;
+      RingPos<C::S> pos;
       bool alive = true;
+      // Both CTAs of a pair feed the leader's MMA: byte counts go to the leader's barrier.
+      uint32_t full_remote[C::S];
+#pragma unroll
+      for (int s = 0; s < C::S; ++s) full_remote[s] = (CG == 2) ? ptx::mapa(bar_full(s), 0) : 0u;
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
         int mt, nt;
         tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
         const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % C::SA;
-          const uint32_t ph = (it / C::SA) & 1;
-          if (!detail::wait_bar<CG == 2>(bar_a_free(s), ph ^ 1, abort_flag, p.status,
-                                         DEV_TIMEOUT_PRODUCER)) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, abort_flag, p.status,
+                                DEV_TIMEOUT_PRODUCER)) {
             alive = false;
             break;
           }
-          const uint32_t dst = smem_base + C::OFF_A + s * C::A_BYTES;
+          const uint32_t dst = smem_base + C::OFF_MAIN + pos.slot * C::STAGE_BYTES;
           if constexpr (CG == 1) {
-            ptx::mbar_arrive_expect_tx(bar_a_full(s), C::A_BYTES);
-            ptx::tma_load_2d(dst, &tm_a, bar_a_full(s), kb * C::BK, m0);
+            ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES);
+            ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
           } else {
-            if (leader) ptx::mbar_arrive_expect_tx(bar_a_full(s), 2 * C::A_BYTES);
-            ptx::tma_load_2d_pair(dst, &tm_a, ptx::mapa(bar_a_full(s), 0), kb * C::BK, m0);
+            if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * C::A_BYTES);
+            uint32_t remote = full_remote[0];
+#pragma unroll
+            for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
+            ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
           }
+          pos.advance();
         }
       }
       if (!alive) {
@@ -287,23 +301,22 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else if (warp == C::WARP_B_PRODUCER) {
     // ===================== TMA producer: packed int4 weights =====================
     if (lane == 0) {
-      uint32_t it = 0;
+      RingPos<C::SB> pos;
       bool alive = true;
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
         int mt, nt;
         tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
         const int n0 = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % C::SB;
-          const uint32_t ph = (it / C::SB) & 1;
-          if (!detail::wait_bar<false>(bar_bp_free(s), ph ^ 1, abort_flag, p.status,
-                                       DEV_TIMEOUT_PRODUCER)) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!detail::wait_bar(bar_bp_free(pos.slot), pos.phase ^ 1, abort_flag, p.status,
+                                DEV_TIMEOUT_PRODUCER)) {
             alive = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(bar_bp_full(s), C::BP_BYTES);
-          ptx::tma_load_2d(smem_base + C::OFF_BP + s * C::BP_BYTES, &tm_w, bar_bp_full(s),
-                           kb * (C::BK / 2), n0);
+          ptx::mbar_arrive_expect_tx(bar_bp_full(pos.slot), C::BP_BYTES);
+          ptx::tma_load_2d(smem_base + C::OFF_BP + pos.slot * C::BP_BYTES, &tm_w,
+                           bar_bp_full(pos.slot), kb * (C::BK / 2), n0);
+          pos.advance();
         }
       }
       if (!alive) {
@@ -314,47 +327,45 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp == C::WARP_MMA) {
     // ===================== MMA issuer =====================
+    // One thread issues every MMA of the group, so its loop is kept to one barrier probe, four
+    // MMAs and one commit per stage.
     if (lane == 0 && (CG == 1 || leader)) {
       constexpr uint32_t idesc = make_i8_idesc(C::BM * CG, C::BN);
-      uint32_t it = 0;
+      const uint64_t adesc0 = make_kmajor_sw128_desc(smem_base + C::OFF_MAIN);
+      const uint64_t bdesc0 = make_kmajor_sw128_desc(smem_base + C::OFF_MAIN + C::A_BYTES);
+      RingPos<C::S> pos;
       uint32_t local_tile = 0;
       bool alive = true;
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
         const uint32_t ab = local_tile & 1;
         const uint32_t aph = (local_tile >> 1) & 1;
-        if (!detail::wait_bar<CG == 2>(bar_acc_free(ab), aph ^ 1, abort_flag, p.status,
-                                       DEV_TIMEOUT_MMA)) {
+        if (!detail::wait_bar(bar_acc_free(ab), aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA)) {
           alive = false;
           break;
         }
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + ab * C::BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sa = it % C::SA, su = it % C::SU;
-          const uint32_t pha = (it / C::SA) & 1, phu = (it / C::SU) & 1;
-          if (!detail::wait_bar<CG == 2>(bar_a_full(sa), pha, abort_flag, p.status,
-                                         DEV_TIMEOUT_MMA) ||
-              !detail::wait_bar<CG == 2>(bar_bu_full(su), phu, abort_flag, p.status,
-                                         DEV_TIMEOUT_MMA)) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!detail::wait_bar(bar_full(pos.slot), pos.phase, abort_flag, p.status,
+                                DEV_TIMEOUT_MMA)) {
             alive = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint64_t adesc = make_kmajor_sw128_desc(smem_base + C::OFF_A + sa * C::A_BYTES);
-          const uint64_t bdesc = make_kmajor_sw128_desc(smem_base + C::OFF_BU + su * C::BU_BYTES);
+          const uint32_t off = pos.slot * (C::STAGE_BYTES >> 4);
+          const uint64_t adesc = adesc0 + off;
+          const uint64_t bdesc = bdesc0 + off;
 #pragma unroll
           for (int k = 0; k < C::BK / 32; ++k) {
             // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
             ptx::mma_i8_ss<CG>(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc,
                                (kb > 0 || k > 0) ? 1u : 0u);
           }
-          if constexpr (CG == 1) {
-            ptx::mma_commit(bar_a_free(sa));
-            ptx::mma_commit(bar_bu_free(su));
-          } else {
-            ptx::mma_commit_pair(bar_a_free(sa), 0x3);
-            ptx::mma_commit_pair(bar_bu_free(su), 0x3);
-          }
+          if constexpr (CG == 1)
+            ptx::mma_commit(bar_consumed(pos.slot));
+          else
+            ptx::mma_commit_pair(bar_consumed(pos.slot), 0x3);
+          pos.advance();
         }
         if (alive) {
           if constexpr (CG == 1)
@@ -366,35 +377,38 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp < C::WARP_EPI0) {
     // ===================== int4 -> int8 weight unpack =====================
-    const int tid_u = static_cast<int>(threadIdx.x) - 32 * C::WARP_UNPACK0;  // 0..127
+    const int tid_u = static_cast<int>(threadIdx.x) - 32 * C::WARP_UNPACK0;
     const uint32_t row_x = static_cast<uint32_t>((tid_u >> 2) & 7);
     const uint32_t c2 = static_cast<uint32_t>(tid_u & 3) * 2;
     const uint32_t hi_off = ((c2 ^ row_x) << 4);
     const uint32_t lo_off = (((c2 + 1) ^ row_x) << 4);
-    uint32_t it = 0;
+    RingPos<C::S> pos;
+    RingPos<C::SB> bpos;
     bool alive = true;
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int sb = it % C::SB, su = it % C::SU;
-        const uint32_t phb = (it / C::SB) & 1, phu = (it / C::SU) & 1;
-        if (!detail::wait_bar<false>(bar_bp_full(sb), phb, abort_flag, p.status,
-                                     DEV_TIMEOUT_UNPACK) ||
-            !detail::wait_bar<CG == 2>(bar_bu_free(su), phu ^ 1, abort_flag, p.status,
-                                       DEV_TIMEOUT_UNPACK)) {
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!detail::wait_bar(bar_bp_full(bpos.slot), bpos.phase, abort_flag, p.status,
+                              DEV_TIMEOUT_UNPACK) ||
+            !detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, abort_flag, p.status,
+                              DEV_TIMEOUT_UNPACK)) {
           alive = false;
           break;
         }
-        const uint32_t bp = smem_base + C::OFF_BP + sb * C::BP_BYTES;
-        const uint32_t bu = smem_base + C::OFF_BU + su * C::BU_BYTES;
+        const uint32_t bp = smem_base + C::OFF_BP + bpos.slot * C::BP_BYTES;
+        const uint32_t bu = smem_base + C::OFF_MAIN + pos.slot * C::STAGE_BYTES + C::A_BYTES;
+        constexpr int ITERS = C::B_ROWS * 4 / C::UNPACK_THREADS;
+        uint4 pk[ITERS];
 #pragma unroll
-        for (int j = 0; j < C::B_ROWS * 4 / 128; ++j) {
-          const int q = tid_u + 128 * j;          // 16-byte packed chunk index in the tile
-          const uint4 pk = detail::lds128(bp + 16u * q);
+        for (int j = 0; j < ITERS; ++j)
+          pk[j] = detail::lds128(bp + 16u * static_cast<uint32_t>(tid_u + C::UNPACK_THREADS * j));
+#pragma unroll
+        for (int j = 0; j < ITERS; ++j) {
+          const int q = tid_u + C::UNPACK_THREADS * j;  // 16-byte packed chunk index in the tile
           uint4 hi, lo;
-          hi.x = pk.x & 0xF0F0F0F0u; lo.x = (pk.x << 4) & 0xF0F0F0F0u;
-          hi.y = pk.y & 0xF0F0F0F0u; lo.y = (pk.y << 4) & 0xF0F0F0F0u;
-          hi.z = pk.z & 0xF0F0F0F0u; lo.z = (pk.z << 4) & 0xF0F0F0F0u;
-          hi.w = pk.w & 0xF0F0F0F0u; lo.w = (pk.w << 4) & 0xF0F0F0F0u;
+          hi.x = pk[j].x & 0xF0F0F0F0u; lo.x = (pk[j].x << 4) & 0xF0F0F0F0u;
+          hi.y = pk[j].y & 0xF0F0F0F0u; lo.y = (pk[j].y << 4) & 0xF0F0F0F0u;
+          hi.z = pk[j].z & 0xF0F0F0F0u; lo.z = (pk[j].z << 4) & 0xF0F0F0F0u;
+          hi.w = pk[j].w & 0xF0F0F0F0u; lo.w = (pk[j].w << 4) & 0xF0F0F0F0u;
           const uint32_t row_addr = bu + 128u * static_cast<uint32_t>(q >> 2);
           detail::sts128(row_addr + hi_off, hi);
           detail::sts128(row_addr + lo_off, lo);
@@ -403,12 +417,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::mbar_arrive(bar_bp_free(sb));
+          ptx::mbar_arrive(bar_bp_free(bpos.slot));
           if constexpr (CG == 1)
-            ptx::mbar_arrive(bar_bu_full(su));
+            ptx::mbar_arrive(bar_full(pos.slot));
           else
-            ptx::mbar_arrive_cluster(bar_bu_full(su), 0);
+            ptx::mbar_arrive_cluster(bar_full(pos.slot), 0);
         }
+        pos.advance();
+        bpos.advance();
       }
     }
   } else {
@@ -426,8 +442,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int n0 = nt * C::BN;
       const uint32_t ab = local_tile & 1;
       const uint32_t aph = (local_tile >> 1) & 1;
-      if (!detail::wait_bar<CG == 2>(bar_acc_full(ab), aph, abort_flag, p.status,
-                                     DEV_TIMEOUT_EPILOGUE)) {
+      if (!detail::wait_bar(bar_acc_full(ab), aph, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
         alive = false;
         break;
       }

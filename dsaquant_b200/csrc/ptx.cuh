@@ -69,13 +69,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                : "memory");
 }
 
-// One non-blocking probe of the phase with the given parity.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// Non-suspending probe of the phase with the given parity (cheapest when it is already complete).
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
@@ -84,8 +84,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Same, acquire at cluster scope (the barrier is also signalled from the peer CTA).
-__device__ __forceinline__ bool mbar_test_cluster(uint32_t bar, uint32_t parity) {
+// One potentially suspending probe (returns early when the phase completes).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
