@@ -174,6 +174,40 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
   return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
+// ---- scratch of b200w4a4_linear_noalloc -------------------------------------------------
+// Quantised activation codes (int8 [M,K]) followed by the per-token scales (fp32 [M]).
+constexpr size_t kNoAllocCodeBytes = static_cast<size_t>(8) << 20;  // M * K <= 8 Mi codes
+constexpr int kNoAllocMaxRows = 8192;                               // M <= 8192 tokens
+static __device__ __align__(256) uint8_t
+    g_noalloc_scratch[kNoAllocCodeBytes + kNoAllocMaxRows * sizeof(float)];
+
+struct NoAllocState {
+  std::once_flag once;
+  int err = B200W4A4_OK;
+  uint8_t* base = nullptr;  // device address of g_noalloc_scratch on this device
+};
+NoAllocState g_noalloc[kMaxDevices];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address:
+// the address valid on the current device has to be asked for, once per device.
+int noalloc_scratch(uint8_t** base) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B200W4A4_ECUDA;
+  if (dev < 0 || dev >= kMaxDevices) return B200W4A4_EINVAL;
+  NoAllocState& st = g_noalloc[dev];
+  std::call_once(st.once, [&st] {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      st.err = B200W4A4_ECUDA;
+      return;
+    }
+    st.base = static_cast<uint8_t*>(ptr);
+  });
+  *base = st.base;
+  return st.err;
+}
+
 }  // namespace
 
 extern "C" {
@@ -190,6 +224,7 @@ const char* b200w4a4_strerror(int code) {
     case B200W4A4_ECUDA: return "CUDA runtime or driver call failed";
     case B200W4A4_EWORKSPACE: return "workspace too small";
     case B200W4A4_EDEVICE: return "a kernel recorded a device-side time-out";
+    case B200W4A4_ELIMIT: return "activation too large for the built-in scratch of the no-alloc entry point";
     default: return "unknown b200w4a4 error code";
   }
 }
@@ -336,6 +371,30 @@ int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* 
   float* act_scale =
       reinterpret_cast<float*>(ws + ((static_cast<size_t>(M) * K + 255) & ~static_cast<size_t>(255)));
   int rc = b200w4a4_quantize_act(x, x_dtype, qact, B200W4A4_QACT_INT8, act_scale, M, K, clip, stream);
+  if (rc != B200W4A4_OK) return rc;
+  return b200w4a4_gemm(qact, act_scale, w_b200, w_scale, bias, out, nullptr, M, N, K, stream);
+}
+
+size_t b200w4a4_linear_noalloc_max_codes(void) { return kNoAllocCodeBytes; }
+
+int b200w4a4_linear_noalloc_max_rows(void) { return kNoAllocMaxRows; }
+
+// Quantise + GEMM with the intermediate codes and scales held in a device array that is part
+// of the library image, for callers that must not allocate device memory at all.
+int b200w4a4_linear_noalloc(const void* x, int x_dtype, const void* w_b200, const void* w_scale,
+                            const void* bias, void* out, int M, int N, int K, float clip,
+                            void* stream) {
+  if (M < 1 || K < 64 || (K % 64) != 0) return B200W4A4_ESHAPE;
+  if (M > kNoAllocMaxRows || static_cast<size_t>(M) * static_cast<size_t>(K) > kNoAllocCodeBytes)
+    return B200W4A4_ELIMIT;
+  uint8_t* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc != B200W4A4_OK) return rc;
+  void* qact = base;
+  float* act_scale = reinterpret_cast<float*>(base + kNoAllocCodeBytes);
+  // Nothing in the scratch has to start at zero: the quantiser rewrites codes [M,K] and scales
+  // [M] before the GEMM reads them, and the GEMM's tensor map ends at row M.
+  rc = b200w4a4_quantize_act(x, x_dtype, qact, B200W4A4_QACT_INT8, act_scale, M, K, clip, stream);
   if (rc != B200W4A4_OK) return rc;
   return b200w4a4_gemm(qact, act_scale, w_b200, w_scale, bias, out, nullptr, M, N, K, stream);
 }

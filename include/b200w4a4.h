@@ -33,6 +33,7 @@ extern "C" {
 #define B200W4A4_ECUDA (-5)       /* CUDA runtime / driver call failed */
 #define B200W4A4_EWORKSPACE (-6)  /* workspace too small */
 #define B200W4A4_EDEVICE (-7)     /* a kernel recorded a device-side time-out */
+#define B200W4A4_ELIMIT (-8)      /* beyond the built-in scratch of b200w4a4_linear_noalloc */
 
 /* activation dtypes accepted by the quantiser */
 #define B200W4A4_F16 0
@@ -115,6 +116,34 @@ size_t b200w4a4_linear_workspace_bytes(int M, int K);
 int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* w_scale,
                     const void* bias, void* out, void* workspace, size_t workspace_bytes, int M,
                     int N, int K, float clip, void* stream);
+
+/* Same result as b200w4a4_linear, for callers that cannot allocate device memory.
+ * (No counterpart in the reference, whose ops allocate their intermediates with
+ * torch::empty on every call.)
+ *
+ * Some hosts of this library may not call cudaMalloc or any allocator at the point where
+ * they run a layer: code running inside a memory-pool or arena that was sized up front, a
+ * real-time or serving loop that forbids allocator calls after start-up, an embedding
+ * runtime that hands out device memory itself and has none to spare for a workspace.
+ * b200w4a4_linear needs a caller-provided workspace for the quantised activations; this
+ * entry point keeps that intermediate in an array that is part of the library image instead
+ * (8 MiB of codes + 32 KiB of scales; every GPU that loads the library holds it until the
+ * process exits).  The caller still passes x, the repacked weight, scales, bias and out.
+ *
+ * Limits: M <= b200w4a4_linear_noalloc_max_rows() (8192) and
+ * M * K <= b200w4a4_linear_noalloc_max_codes() (8 Mi, e.g. 512 x 13824 or 1638 x 5120);
+ * larger shapes return B200W4A4_ELIMIT and launch nothing.
+ * It calls no cudaMalloc / cudaFree or other allocating routine.  The first call on a device
+ * looks up the array's address on that device (and does this library's usual one-time
+ * per-device set-up); make that first call before any stream capture begins.
+ * All calls share the one array, which keeps whatever the last call left in it: two calls
+ * that overlap on the GPU (different streams, or the same stream from two threads without
+ * ordering) race on it.  Calls on one stream are ordered and safe. */
+int b200w4a4_linear_noalloc(const void* x, int x_dtype, const void* w_b200, const void* w_scale,
+                            const void* bias, void* out, int M, int N, int K, float clip,
+                            void* stream);
+size_t b200w4a4_linear_noalloc_max_codes(void);
+int b200w4a4_linear_noalloc_max_rows(void);
 
 /* ---- helpers ------------------------------------------------------------ */
 
