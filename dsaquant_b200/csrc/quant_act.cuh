@@ -11,6 +11,8 @@
 //   amax  = max_k |x[m,k]|
 //   s[m]  = (max(amax, 1e-5f) / 7.0f) * clip
 //   q     = clamp(rint(x / s[m]), -8, 7)            (true division, ties to even)
+// The kernel evaluates q with a reciprocal multiply and falls back to the division for
+// values near a rounding tie, which provably yields the same integer (see chunk_codes).
 // which is UniformQuantizer's symmetric path on an fp32 2-D input
 // (vdm_infer/quantization/quant_linear.py:43-48, :64-66) with the clip applied
 // to the scale as the kernel path does (vdm_w4a4_kernel.cu:478).
@@ -31,61 +33,120 @@ enum : int {
 
 namespace detail {
 
+// A chunk is 8 consecutive values of a row, kept in registers in its storage format.
 template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+struct Chunk;
 
 template <>
-__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
-  const uint4 r = __ldcs(reinterpret_cast<const uint4*>(p));
-  const __half2* h = reinterpret_cast<const __half2*>(&r);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(h[i]);
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
+struct Chunk<__half> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __half* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  // max |v| over the chunk, folded into a running packed maximum (no conversion needed:
+  // the maximum of fp16 values is one of them).
+  __device__ __forceinline__ void absmax(float& m) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+    __half2 a = __hmax2(__habs2(h[0]), __habs2(h[1]));
+    __half2 b = __hmax2(__habs2(h[2]), __habs2(h[3]));
+    a = __hmax2(a, b);
+    m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
   }
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 r = __ldcs(reinterpret_cast<const uint4*>(p));
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  __device__ __forceinline__ void values(float (&v)[8]) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
   }
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
+};
 
-// clamp(rint(x / s), -8, 7) as the low byte of the result (two's complement).
-// Clamping first is equivalent because the bounds are integers; adding
-// 1.5 * 2^23 rounds to nearest-even and leaves the integer in the low mantissa bits.
-__device__ __forceinline__ uint32_t code_bits(float x, float s) {
-  float t = x / s;
-  t = fminf(fmaxf(t, -8.0f), 7.0f);
-  return __float_as_uint(t + 12582912.0f);
-}
+template <>
+struct Chunk<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    raw = __ldcs(reinterpret_cast<const uint4*>(p));
+  }
+  __device__ __forceinline__ void values(float (&v)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  __device__ __forceinline__ void absmax(float& m) const {
+    float v[8];
+    values(v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(v[e]));
+  }
+};
+
+template <>
+struct Chunk<float> {
+  float4 lo, hi;
+  __device__ __forceinline__ void load(const float* p) {
+    lo = __ldcs(reinterpret_cast<const float4*>(p));
+    hi = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void values(float (&v)[8]) const {
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+    v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+  }
+  __device__ __forceinline__ void absmax(float& m) const {
+    float v[8];
+    values(v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(v[e]));
+  }
+};
+
+constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to nearest-even
 
 __device__ __forceinline__ float row_scale(float amax, float clip) {
   return __fmul_rn(__fdiv_rn(fmaxf(amax, 1e-5f), 7.0f), clip);
 }
 
-template <int QOUT>
-__device__ __forceinline__ void store8(void* q, size_t row, int K, int chunk, const float (&v)[8],
-                                       float s) {
-  uint32_t c[8];
+// Bits of (clamp(rint(x / s), -8, 7) + magic): the code is the low byte (two's complement).
+// Clamping first is equivalent because the bounds are integers.
+__device__ __forceinline__ uint32_t code_bits_div(float x, float s) {
+  float t = __fdiv_rn(x, s);
+  t = fminf(fmaxf(t, -8.0f), 7.0f);
+  return __float_as_uint(t + kRoundMagic);
+}
+
+// Eight codes of one chunk.  Fast path: t = x * r with r = RN(1/s) instead of the division.
+// |t - x/s| <= |x/s| * 2^-23 < 2^-19 in the unclamped range, so rint(t) can differ from
+// rint(fl(x/s)) only if t lies within 2^-18 of a half-integer; such chunks (about one in
+// ten thousand) are redone with the IEEE division, which makes the result identical to
+// clamp(rint(x / s)) for every input.  `exact_only` rows (scale so large that 1/s would be
+// subnormal) always take the division.
+__device__ __forceinline__ void chunk_codes(const float (&v)[8], float s, float r, bool exact_only,
+                                            uint32_t (&c)[8]) {
+  float worst = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) c[i] = code_bits(v[i], s);
+  for (int i = 0; i < 8; ++i) {
+    float t = __fmul_rn(v[i], r);
+    t = fminf(fmaxf(t, -8.0f), 7.0f);
+    const float y = __fadd_rn(t, kRoundMagic);
+    const float d = __fsub_rn(t, __fsub_rn(y, kRoundMagic));  // exact distance to the chosen integer
+    worst = fmaxf(worst, fabsf(d));
+    c[i] = __float_as_uint(y);
+  }
+  if (exact_only || worst >= 0.5f - 3.814697265625e-06f) {  // 2^-18
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = code_bits_div(v[i], s);
+  }
+}
+
+template <int QOUT>
+__device__ __forceinline__ void store_codes(void* q, size_t row, int K, int chunk,
+                                            const uint32_t (&c)[8]) {
   if constexpr (QOUT == QOUT_INT8) {
     uint2 o;
-    o.x = (c[0] & 0xFF) | ((c[1] & 0xFF) << 8) | ((c[2] & 0xFF) << 16) | (c[3] << 24);
-    o.y = (c[4] & 0xFF) | ((c[5] & 0xFF) << 8) | ((c[6] & 0xFF) << 16) | (c[7] << 24);
+    o.x = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+    o.y = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
     *reinterpret_cast<uint2*>(static_cast<uint8_t*>(q) + row * K + 8 * static_cast<size_t>(chunk)) = o;
   } else {
     uint32_t o = 0;
@@ -94,6 +155,12 @@ __device__ __forceinline__ void store8(void* q, size_t row, int K, int chunk, co
     *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(q) + row * (K / 2) +
                                  4 * static_cast<size_t>(chunk)) = o;
   }
+}
+
+// Reciprocal used by the fast path, and whether the row must use the division throughout.
+__device__ __forceinline__ float scale_reciprocal(float s, bool& exact_only) {
+  exact_only = !(s < 1.0e30f);  // also true for NaN / inf scales
+  return exact_only ? 0.0f : __frcp_rn(s);
 }
 
 }  // namespace detail
@@ -111,16 +178,17 @@ quant_act_rows_kernel(const T* __restrict__ x, void* __restrict__ q, float* __re
   const int nchunks = K >> 3;
   const T* xr = x + (row_ok ? row : 0) * static_cast<long long>(K);
 
-  float v[NCH][8];
+  detail::Chunk<T> ch[NCH];
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
-    if (row_ok && c < nchunks) {
-      detail::load8<T>(xr + 8 * c, v[i]);
+    if (row_ok && c < nchunks) ch[i].load(xr + 8 * c);
+  }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
-    }
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    if (row_ok && c < nchunks) ch[i].absmax(amax);
   }
   constexpr int W = TPR < 32 ? TPR : 32;
 #pragma unroll
@@ -136,13 +204,21 @@ quant_act_rows_kernel(const T* __restrict__ x, void* __restrict__ q, float* __re
 #pragma unroll
     for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, wmax[w0 + w]);
   }
-  const float s = detail::row_scale(amax, clip);
   if (!row_ok) return;
+  const float s = detail::row_scale(amax, clip);
+  bool exact_only;
+  const float r = detail::scale_reciprocal(s, exact_only);
   if (t == 0) scale[row] = s;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
-    if (c < nchunks) detail::store8<QOUT>(q, static_cast<size_t>(row), K, c, v[i], s);
+    if (c < nchunks) {
+      float v[8];
+      uint32_t codes[8];
+      ch[i].values(v);
+      detail::chunk_codes(v, s, r, exact_only, codes);
+      detail::store_codes<QOUT>(q, static_cast<size_t>(row), K, c, codes);
+    }
   }
 }
 
@@ -157,10 +233,9 @@ quant_act_long_rows_kernel(const T* __restrict__ x, void* __restrict__ q,
   const T* xr = x + row * static_cast<long long>(K);
   float amax = 0.0f;
   for (int c = threadIdx.x; c < nchunks; c += 256) {
-    float v[8];
-    detail::load8<T>(xr + 8 * c, v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    detail::Chunk<T> ch;
+    ch.load(xr + 8 * c);
+    ch.absmax(amax);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -171,11 +246,17 @@ quant_act_long_rows_kernel(const T* __restrict__ x, void* __restrict__ q,
 #pragma unroll
   for (int w = 1; w < 8; ++w) amax = fmaxf(amax, wmax[w]);
   const float s = detail::row_scale(amax, clip);
+  bool exact_only;
+  const float r = detail::scale_reciprocal(s, exact_only);
   if (threadIdx.x == 0) scale[row] = s;
   for (int c = threadIdx.x; c < nchunks; c += 256) {
+    detail::Chunk<T> ch;
     float v[8];
-    detail::load8<T>(xr + 8 * c, v);
-    detail::store8<QOUT>(q, static_cast<size_t>(row), K, c, v, s);
+    uint32_t codes[8];
+    ch.load(xr + 8 * c);
+    ch.values(v);
+    detail::chunk_codes(v, s, r, exact_only, codes);
+    detail::store_codes<QOUT>(q, static_cast<size_t>(row), K, c, codes);
   }
 }
 
