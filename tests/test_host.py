@@ -1,0 +1,267 @@
+"""CPU-only tests: the C-ABI library loads and exports what the header declares, the python
+mirror keeps the reference's interface, the fake-quant branch reproduces the reference fixtures,
+and the packed-checkpoint loader handles the vdm_w4a4_packed_v1 format."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from _cases import CASES, make_case
+from oracle import w4a4_oracle as orc
+
+ROOT = Path(__file__).resolve().parent.parent
+GOLD = Path(__file__).resolve().parent / "golden"
+QPARAMS = {"w": {"bit": 4, "sym": True, "granularity": "per_channel", "group_size": -1,
+                 "round_zero": True, "use_grad_scaling": True, "cali": "mse"},
+           "act": {"bit": 4, "sym": True}}
+
+
+def test_library_exports_every_declared_symbol():
+    from dsaquant_b200 import _lib
+
+    header = (ROOT / "include" / "b200w4a4.h").read_text()
+    declared = set(re.findall(r"\b(b200w4a4_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) == 17
+    lib = _lib.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == declared
+    assert lib.b200w4a4_version() == 1 == int(re.search(r"B200W4A4_ABI_VERSION (\d+)", header).group(1))
+
+
+def test_host_only_entry_points():
+    from dsaquant_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.b200w4a4_repack_bytes(1536, 1536) == 1536 * 768
+    assert lib.b200w4a4_repack_bytes(100, 64) == 0 and lib.b200w4a4_repack_bytes(128, 96) == 0
+    assert lib.b200w4a4_qact_bytes(257, 1536, 0) == 257 * 1536
+    assert lib.b200w4a4_qact_bytes(257, 1536, 1) == 257 * 768
+    assert lib.b200w4a4_qact_bytes(0, 1536, 0) == 0
+    ws = lib.b200w4a4_linear_workspace_bytes(257, 1536)
+    assert ws >= 257 * 1536 + 257 * 4 and ws % 256 == 0
+    assert lib.b200w4a4_linear_noalloc_max_codes() == 8 << 20
+    assert lib.b200w4a4_set_cta_group(3) == -1
+    for code in range(0, -9, -1):
+        text = lib.b200w4a4_strerror(code).decode()
+        assert text and "unknown" not in text
+    assert "unknown" in lib.b200w4a4_strerror(-99).decode()
+    # argument checks come before any CUDA call
+    assert lib.b200w4a4_gemm(None, None, None, None, None, None, None, 1, 128, 64, None) == -1
+    assert lib.b200w4a4_linear_noalloc(None, 0, None, None, None, None, 9000, 128, 64, 1.0, None) == -8
+
+
+def test_arch_selection_gains_sm100a(monkeypatch):
+    from dsaquant_b200.kernels import vdm_w4a4 as v
+
+    monkeypatch.delenv("TORCH_CUDA_ARCH_LIST", raising=False)
+    for alias in ("b200", "blackwell", "sm100", "sm100a", "sm_100a", "10.0", "10.0a"):
+        monkeypatch.setenv("VDM_W4A4_TARGET_ARCH", alias)
+        assert v._detect_arch_list() == "10.0a"
+    monkeypatch.setenv("TORCH_CUDA_ARCH_LIST", "10.0a")
+    cfg = v.build_config()
+    assert set(cfg) == {"cuda_home", "torch_cuda", "arch_list", "arch_tag", "build_dir", "extension_name"}
+    assert cfg["arch_tag"] == "sm100a"
+    assert v._arch_tag("8.6;10.0a+PTX") == "sm86_sm100aptx"
+    monkeypatch.setenv("TORCH_CUDA_ARCH_LIST", "8.6")
+    with pytest.raises(RuntimeError):
+        v._load_ext()
+    assert (v.BLOCK_M, v.BLOCK_N, v.WARP_K) == (256, 128, 64)
+
+
+def test_wrapper_rejects_cpu_tensors_and_bad_shapes():
+    from dsaquant_b200.kernels import vdm_w4a4 as v
+
+    x = torch.zeros(4, 128)
+    qw = torch.zeros(128, 64, dtype=torch.uint8)
+    ws = torch.zeros(128, 2, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        v.linear_vdm_w4a4(x, qw, ws)
+    with pytest.raises(RuntimeError):
+        v.pack_weight_with_scale(torch.zeros(128, 64), torch.ones(128))
+    with pytest.raises(ValueError, match="multiple of 64"):
+        v._check_linear_shapes(torch.zeros(4, 96), qw, ws)
+    with pytest.raises(ValueError, match="multiple of 128"):
+        v._check_linear_shapes(x, torch.zeros(100, 64, dtype=torch.uint8), ws)
+    with pytest.raises(ValueError, match=r"\[N, K/2\]"):
+        v._check_linear_shapes(x, torch.zeros(128, 32, dtype=torch.uint8), ws)
+    with pytest.raises(ValueError, match=r"\[N, K/64\]"):
+        v._check_linear_shapes(x, qw, torch.zeros(128, 3, dtype=torch.float16))
+
+
+@pytest.mark.parametrize("name", ["tiny", "cfg0"])
+def test_fake_quant_branch_reproduces_reference_fixture(name):
+    """The mirror's PyTorch branch must equal the reference's own fake-quant forward."""
+    from dsaquant_b200.quantization.quant_linear import QuantLinear
+
+    seed, M, K, N, kw, clip = CASES[name]
+    g = np.load(GOLD / f"{name}.npz")
+    x16, w16, b16 = make_case(seed, M, K, N, **kw)
+    lin = nn.Linear(K, N)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(w16).float())
+        lin.bias.copy_(torch.from_numpy(b16).float())
+    ql = QuantLinear(lin, {"w": "lsq", "act": "dynamic"}, QPARAMS)
+    with torch.no_grad():
+        ql.wquantizer(ql.weight.detach())
+        ql.wquantizer.scale.copy_(ql.wquantizer.scale.half().float())
+        ql.set_quant_state(True, True)
+        out = ql(torch.from_numpy(x16).float()).numpy()
+    np.testing.assert_array_equal(ql.aquantizer.scale.reshape(-1).numpy(), g["a_scale"])
+    if "ref_out_f32" in g.files:
+        np.testing.assert_array_equal(out, g["ref_out_f32"])
+    else:
+        np.testing.assert_array_equal(out[::61, ::53], g["ref_out_f32_sample"])
+    # second call keeps the first call's scale, like the reference (init stays True)
+    assert ql.aquantizer.init
+    with pytest.raises(NotImplementedError):
+        ql.set_hadamard(True)
+    assert "use_vdm_kernel=False" in ql.extra_repr()
+
+
+def test_fakequant_cpu_port_matches_oracle():
+    from oracle.fakequant_cpu import fakequant_linear
+
+    x16, w16, b16 = make_case(3, 64, 256, 128)
+    ws = orc.weight_scale_absmax(w16)
+    ref = orc.linear_w4a4(x16, orc.quantize_weight(w16, ws), ws, b16, 1.0)
+    got = fakequant_linear(torch.from_numpy(x16).float(), torch.from_numpy(w16).float(),
+                           torch.from_numpy(ws).float(), torch.from_numpy(b16).float(), 1.0).numpy()
+    np.testing.assert_allclose(got, ref["out"].astype(np.float32), rtol=1e-2, atol=5e-3)
+
+
+class _TinyAttn(nn.Module):
+    def __init__(self, dim):
+        super().__init__()
+        self.to_q, self.to_k, self.to_v = nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim)
+        self.cross_attention_dim_head = None
+
+
+class _TinyModel(nn.Module):
+    def __init__(self, dim=128):
+        super().__init__()
+        self.embed = nn.Linear(8, dim)            # stays fp
+        self.blocks = nn.ModuleList([_TinyAttn(dim)])
+
+
+def _quantize_blocks(model, cls):
+    for blk in model.blocks:
+        for name in ("to_q", "to_k", "to_v"):
+            setattr(blk, name, cls(getattr(blk, name), {"w": "lsq", "act": "dynamic"}, QPARAMS))
+
+
+def _packed_state(model, rng, legacy=False):
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()
+             if ".wquantizer." not in k and ".aquantizer." not in k}
+    for name, mod in model.named_modules():
+        if type(mod).__name__ != "QuantLinear":
+            continue
+        n, k = mod.out_features, mod.in_features
+        codes = rng.integers(-8, 8, size=(n, k), dtype=np.int8)
+        scale = (rng.random(n) * 0.01 + 0.001).astype(np.float16)
+        prefix = "diy_" if legacy else "vdm_"
+        state[f"{name}.{prefix}weight_packed"] = torch.from_numpy(orc.pack_weight_v1(codes))
+        state[f"{name}.{prefix}weight_scale_packed"] = torch.from_numpy(orc.pack_wscale_v1(scale, k))
+        state[f"{name}.{prefix}weight_scale"] = torch.from_numpy(scale)
+        del state[f"{name}.weight"]
+    return state
+
+
+@pytest.mark.parametrize("legacy", [False, True])
+def test_packed_checkpoint_round_trip_on_cpu(tmp_path, legacy):
+    from dsaquant_b200.checkpoints import packed_checkpoint as pc
+    from dsaquant_b200.quantization.quant_linear import QuantLinear
+
+    rng = np.random.default_rng(1)
+    src = _TinyModel()
+    _quantize_blocks(src, QuantLinear)
+    fmt = pc._LEGACY_PACKED_CHECKPOINT_FORMAT if legacy else pc.PACKED_CHECKPOINT_FORMAT
+    ckpt = {"format": fmt, "metadata": {"note": "synthetic"}, "model": _packed_state(src, rng, legacy)}
+    path = tmp_path / "packed.pt"
+    torch.save(ckpt, path)
+    loaded = pc.load_quant_checkpoint(str(path), dcp_loader=None)
+    assert pc.is_packed_checkpoint(loaded) and not pc.is_packed_checkpoint({"format": "other", "model": {}})
+
+    model = _TinyModel()
+    _quantize_blocks(model, QuantLinear)
+    missing, unexpected = pc.load_packed_quantized_model(
+        model, loaded, quant_linear_cls=QuantLinear, dtype=torch.float16, device=torch.device("cpu"),
+        require_vdm_kernel=False, repack_for_b200=False)
+    assert missing == [] and unexpected == []
+    q = model.blocks[0].to_q
+    assert q.use_vdm_kernel and q.weight is None and q.wquantizer is None and q.aquantizer is None
+    assert q.vdm_weight_packed.dtype == torch.uint8 and q.vdm_weight_packed.shape == (128, 64)
+    assert q.vdm_weight_scale_packed.shape == (128, 2) and q.vdm_weight_scale.shape == (128,)
+    assert q._bias_half.dtype == torch.float16 and model.embed.weight.dtype == torch.float16
+    key = "blocks.0.to_q." + ("diy_" if legacy else "vdm_") + "weight_packed"
+    assert torch.equal(q.vdm_weight_packed, ckpt["model"][key])
+
+    pc.enable_fused_qkv(model, quant_linear_cls=QuantLinear, attention_cls=_TinyAttn, use_fused_qkv=True)
+    assert model.blocks[0].use_fused_qkv_kernel and model.blocks[0].qkv_kernel_backend == "vdm"
+
+    # writer: the saved state has the three buffers + bias and no fp weight / quantizer state
+    out_path = tmp_path / "resaved.pt"
+    pc.save_packed_checkpoint(model, str(out_path), metadata={"a": 1})
+    again = torch.load(out_path, weights_only=True)
+    assert again["format"] == pc.PACKED_CHECKPOINT_FORMAT and again["metadata"] == {"a": 1}
+    keys = set(again["model"])
+    assert "blocks.0.to_q.vdm_weight_packed" in keys and "blocks.0.to_q.bias" in keys
+    assert not any(k.endswith(".weight") and "blocks" in k for k in keys)
+    assert not any("quantizer" in k or k.endswith("_bias_half") for k in keys)
+
+    # a checkpoint that lacks a buffer is refused
+    broken = dict(ckpt, model={k: v for k, v in ckpt["model"].items() if "to_v" not in k or "scale" not in k})
+    fresh = _TinyModel()
+    _quantize_blocks(fresh, QuantLinear)
+    with pytest.raises(KeyError, match="missing"):
+        pc.load_packed_quantized_model(fresh, broken, quant_linear_cls=QuantLinear, dtype=torch.float16,
+                                       device=torch.device("cpu"), require_vdm_kernel=False)
+    with pytest.raises(ValueError, match="Unsupported checkpoint format"):
+        pc.load_packed_quantized_model(fresh, {"format": "x", "model": {}}, quant_linear_cls=QuantLinear,
+                                       dtype=torch.float16, device=torch.device("cpu"))
+
+
+def test_fused_qkv_cache_concatenates_v1_buffers():
+    from dsaquant_b200 import attention_qkv as aq
+    from dsaquant_b200.quantization.quant_linear import QuantLinear
+
+    rng = np.random.default_rng(2)
+    attn = _TinyAttn(128)
+    _quantize_blocks(type("M", (), {"blocks": [attn]})(), QuantLinear)
+    codes = []
+    for lin, has_bias in ((attn.to_q, True), (attn.to_k, False), (attn.to_v, True)):
+        c = rng.integers(-8, 8, size=(128, 128), dtype=np.int8)
+        codes.append(c)
+        lin.register_buffer("vdm_weight_packed", torch.from_numpy(orc.pack_weight_v1(c)))
+        lin.register_buffer("vdm_weight_scale_packed", torch.from_numpy(orc.pack_wscale_v1(np.ones(128, np.float16), 128)))
+        lin._bias_half = torch.ones(128, dtype=torch.float16) if has_bias else None
+    aq._cat_cached(attn, "_vdm_qkv", (attn.to_q, attn.to_k, attn.to_v))
+    np.testing.assert_array_equal(attn._vdm_qkv_weight_packed.numpy(), orc.pack_weight_v1(np.concatenate(codes)))
+    assert attn._vdm_qkv_weight_scale.shape == (384, 2)
+    assert attn._vdm_qkv_bias_half.tolist() == [1.0] * 128 + [0.0] * 128 + [1.0] * 128
+
+
+def test_install_as_vdm_infer_aliases_modules():
+    import sys
+
+    import dsaquant_b200
+
+    saved = {k: v for k, v in sys.modules.items() if k == "vdm_infer" or k.startswith("vdm_infer.")}
+    for k in saved:
+        del sys.modules[k]
+    try:
+        dsaquant_b200.install_as_vdm_infer()
+        from vdm_infer.kernels import vdm_w4a4
+        from vdm_infer.quantization.quant_linear import QuantLinear
+
+        assert vdm_w4a4.__name__ == "dsaquant_b200.kernels.vdm_w4a4"
+        assert QuantLinear.__module__ == "dsaquant_b200.quantization.quant_linear"
+    finally:
+        for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
