@@ -1,0 +1,363 @@
+"""Benchmark harness: a diffusers-free restatement of the Wan DiT denoising forward, used only to
+time and parity-check the full-step configurations (Wan 2.1 1.3B / 14B, Wan 2.2 5B) around the
+W4A4 linear path.  It is NOT part of the product: the product is the linear layer.
+
+Follows, by file:line of the reference,
+  model forward            vdm_infer/models/wan_vdm/modules/model.py:172-360
+  transformer block        vdm_infer/models/wan_vdm/modules/dit_block.py:15-117
+  attention processor      vdm_infer/models/wan_vdm/modules/attention.py:133-216 (RMSNorm across heads,
+                           3-D RoPE, SDPA), fused QKV call site :35-121
+  embeddings / RoPE table  vdm_infer/models/wan_vdm/modules/embedding.py:7-156
+  SDPA op                  vdm_infer/models/base/vdm_attn.py:241-259
+  model shapes             vdm_infer/models/wan_vdm/__init__.py:13-112
+and, for the two diffusers classes whose arithmetic matters (not in the reference tree):
+FP32LayerNorm = LayerNorm evaluated in fp32 and cast back; FeedForward(gelu-approximate) =
+Linear -> tanh-GELU -> Linear.  Weights are random (std 0.02, biases 0, scale/shift tables
+std 0.02, norm weights 1) as the reference's init_weights does; every nn.Linear inside the
+blocks is a W4A4 QuantLinear (10 per block), the patch / condition / output projections stay fp16.
+Attention runs as bf16 SDPA (the benchmark definition; the reference pipeline runs it in fp16).
+
+Two linear back-ends share the same int4 weight codes:
+  "kernel"  dsaquant_b200 QuantLinear in kernel mode (sm_100a library), fused QKV / KV
+  "oracle"  PyTorch fake-quant with per-token dynamic activation scales in fp32 (test reference)
+
+Row sharding (multi-GPU inside one CFG branch): every per-token op runs on this rank's rows;
+self-attention all-gathers K and V of the branch group after RMSNorm + RoPE.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from dsaquant_b200 import sharding
+from dsaquant_b200.attention_qkv import get_qkv_projections
+from dsaquant_b200.quantization.quant_linear import QuantLinear
+
+QPARAMS = {"w": {"bit": 4, "sym": True, "granularity": "per_channel"}, "act": {"bit": 4, "sym": True}}
+KERNEL_CLIP = 0.95
+
+
+@dataclass(frozen=True)
+class WanConfig:
+    name: str
+    dim: int
+    heads: int
+    ffn: int
+    layers: int
+    in_ch: int
+    out_ch: int
+    latent: Tuple[int, int, int, int]          # C, F, H, W of the latent video
+    text_dim: int = 4096
+    text_len: int = 512
+    freq_dim: int = 256
+    patch: Tuple[int, int, int] = (1, 2, 2)
+    eps: float = 1e-6
+
+    @property
+    def tokens(self) -> int:
+        _, f, h, w = self.latent
+        return (f // self.patch[0]) * (h // self.patch[1]) * (w // self.patch[2])
+
+
+CONFIGS = {
+    # Wan 2.1 T2V 1.3B: 81 frames at 480x832 -> latent 16x21x60x104 -> 32760 tokens
+    "wan21_1.3b": WanConfig("wan21_1.3b", 1536, 12, 8960, 30, 16, 16, (16, 21, 60, 104)),
+    # Wan 2.2 TI2V 5B: 121 frames at 704x1280 -> latent 48x31x44x80 -> 27280 tokens
+    "wan22_5b": WanConfig("wan22_5b", 3072, 24, 14336, 30, 48, 48, (48, 31, 44, 80)),
+    # Wan 2.1 T2V 14B
+    "wan21_14b": WanConfig("wan21_14b", 5120, 40, 13824, 40, 16, 16, (16, 21, 60, 104)),
+}
+
+
+def tiny_config(dim=256, heads=2, ffn=512, layers=2, latent=(16, 3, 8, 12)) -> WanConfig:
+    return WanConfig("tiny", dim, heads, ffn, layers, latent[0], latent[0], latent, text_dim=128, text_len=64)
+
+
+# --------------------------------------------------------------------------- linear back-ends
+class OracleW4A4Linear(nn.Module):
+    """PyTorch fake-quant W4A4 linear on the SAME weight codes as a kernel-mode QuantLinear:
+    per-token dynamic activation scale (max(absmax,1e-5)/7*clip, fp32), codes by true division,
+    fp32 matmul of the integer codes, dequant, bias, fp16."""
+
+    def __init__(self, ql: QuantLinear, codes: torch.Tensor):
+        super().__init__()
+        self.register_buffer("codes", codes.float())
+        self.register_buffer("w_scale", ql.vdm_weight_scale.float())
+        self.bias_half = ql._bias_half
+        self.clip = ql.kernel_clip_ratio
+        self.vdm_weight_packed = ql.vdm_weight_packed
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1]).float()
+        s = (x2.abs().amax(dim=1, keepdim=True).clamp(min=1e-5) / 7) * self.clip
+        q = torch.clamp(torch.round(x2 / s), -8, 7)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            acc = q @ self.codes.t()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+        y = acc * (s * self.w_scale[None, :])
+        if self.bias_half is not None:
+            y = y + self.bias_half.float()[None, :]
+        return y.half().reshape(*shape, -1)
+
+
+def _quantize_linear(lin: nn.Linear) -> QuantLinear:
+    """nn.Linear -> kernel-mode QuantLinear (abs-max/7 weight scales, packed on the GPU), the
+    reference's legacy build path (quant_linear.py:136-160)."""
+    ql = QuantLinear(lin, {"w": "lsq", "act": "dynamic"}, QPARAMS).to(lin.weight.device).half()
+    ql.wquantizer(ql.weight.detach())
+    ql.set_quant_state(True, True)
+    ql.enable_vdm_kernel_mode()
+    ql.prepare_b200_weights()
+    return ql
+
+
+# --------------------------------------------------------------------------- model pieces
+def fp32_layer_norm(x: torch.Tensor, eps: float, weight=None, bias=None) -> torch.Tensor:
+    return F.layer_norm(x.float(), (x.shape[-1],), None if weight is None else weight.float(),
+                        None if bias is None else bias.float(), eps)
+
+
+class RMSNormAcrossHeads(nn.Module):
+    def __init__(self, dim: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+def rope_table(head_dim: int, f: int, h: int, w: int, device) -> torch.Tensor:
+    """Complex rotation factors [f*h*w, 1, head_dim/2] (embedding.py:103-156)."""
+    def table(dim, end=1024, theta=10000.0):
+        freqs = 1.0 / (theta ** (torch.arange(0, dim, 2)[: dim // 2].double() / dim))
+        ang = torch.outer(torch.arange(end).double(), freqs)
+        return torch.polar(torch.ones_like(ang), ang)
+    d = head_dim
+    ft, ht, wt = table(d - 2 * (d // 3)), table(d // 3), table(d // 3)
+    out = torch.cat([ft[:f].view(f, 1, 1, -1).expand(f, h, w, -1),
+                     ht[:h].view(1, h, 1, -1).expand(f, h, w, -1),
+                     wt[:w].view(1, 1, w, -1).expand(f, h, w, -1)], dim=-1)
+    return out.reshape(f * h * w, 1, -1).to(torch.complex64).to(device)
+
+
+def apply_rope(x: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
+    """x [1, L, H, D]; freqs [L, 1, D/2] complex64 (attention.py:133-137, fp32 variant)."""
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    return torch.view_as_real(xc * freqs[None]).flatten(3).to(x.dtype)
+
+
+class WanAttention(nn.Module):
+    def __init__(self, cfg: WanConfig, cross: bool):
+        super().__init__()
+        d = cfg.dim
+        self.heads = cfg.heads
+        self.cross_attention_dim_head = d // cfg.heads if cross else None
+        self.to_q, self.to_k, self.to_v, self.to_out = (nn.Linear(d, d) for _ in range(4))
+        self.norm_q = RMSNormAcrossHeads(d, cfg.eps)
+        self.norm_k = RMSNormAcrossHeads(d, cfg.eps)
+        self.use_fused_qkv_kernel = False
+        self.qkv_kernel_backend = None
+
+    def forward(self, x, ctx, freqs, group=None, m_total=None):
+        q, k, v = get_qkv_projections(self, x, ctx)
+        q, k = self.norm_q(q), self.norm_k(k)
+        q, k, v = (t.unflatten(2, (self.heads, -1)) for t in (q, k, v))
+        if freqs is not None:
+            q, k = apply_rope(q, freqs), apply_rope(k, freqs)
+        if group is not None and ctx is None:
+            # row-sharded self-attention: every rank needs all keys and values of its branch
+            k = sharding.all_gather_rows(k.reshape(k.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
+            v = sharding.all_gather_rows(v.reshape(v.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2).bfloat16(), k.transpose(1, 2).bfloat16(),
+                                           v.transpose(1, 2).bfloat16(), dropout_p=0.0, is_causal=False)
+        o = o.transpose(1, 2).flatten(2, 3).to(x.dtype)
+        return self.to_out(o)
+
+
+class WanBlock(nn.Module):
+    def __init__(self, cfg: WanConfig):
+        super().__init__()
+        d = cfg.dim
+        self.eps = cfg.eps
+        self.attn1 = WanAttention(cfg, cross=False)
+        self.attn2 = WanAttention(cfg, cross=True)
+        self.norm2 = nn.LayerNorm(d, cfg.eps, elementwise_affine=True)
+        self.ffn_up = nn.Linear(d, cfg.ffn)
+        self.ffn_down = nn.Linear(cfg.ffn, d)
+        self.scale_shift_table = nn.Parameter(torch.randn(1, 6, d) * 0.02)
+
+    def forward(self, x, ctx, temb6, freqs, group=None, m_total=None):
+        # temb6 [1 or L, 6, D] fp32; the reference materialises it per token (model.py:220-231).
+        mod = self.scale_shift_table.float() + temb6.float()
+        shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (mod[:, i][None] for i in range(6))
+        h = (fp32_layer_norm(x, self.eps) * (1 + scale_msa) + shift_msa).to(x.dtype)
+        x = (x.float() + self.attn1(h, None, freqs, group, m_total).float() * gate_msa).to(x.dtype)
+        h = fp32_layer_norm(x, self.eps, self.norm2.weight, self.norm2.bias).to(x.dtype)
+        x = x + self.attn2(h, ctx, None)
+        h = (fp32_layer_norm(x, self.eps) * (1 + c_scale) + c_shift).to(x.dtype)
+        h = self.ffn_down(F.gelu(self.ffn_up(h), approximate="tanh"))
+        return (x.float() + h.float() * c_gate).to(x.dtype)
+
+
+class WanDiT(nn.Module):
+    def __init__(self, cfg: WanConfig):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.dim
+        p = math.prod(cfg.patch)
+        self.patch_embedding_mlp = nn.Linear(cfg.in_ch * p, d)
+        self.time_embedder = nn.Sequential(nn.Linear(cfg.freq_dim, d), nn.SiLU(), nn.Linear(d, d))
+        self.time_proj = nn.Linear(d, 6 * d)
+        self.text_embedder = nn.Sequential(nn.Linear(cfg.text_dim, d), nn.GELU(approximate="tanh"), nn.Linear(d, d))
+        self.blocks = nn.ModuleList([WanBlock(cfg) for _ in range(cfg.layers)])
+        self.proj_out = nn.Linear(d, cfg.out_ch * p)
+        self.scale_shift_table = nn.Parameter(torch.randn(1, 2, d) * 0.02)
+        self.backend = "fp16"
+
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0):
+        g = torch.Generator(device=self.proj_out.weight.device).manual_seed(seed)
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                m.weight.copy_(torch.randn(m.weight.shape, generator=g, device=m.weight.device) * 0.02)
+                m.bias.zero_()
+        for name, prm in self.named_parameters():
+            if name.endswith("scale_shift_table"):
+                prm.copy_(torch.randn(prm.shape, generator=g, device=prm.device) * 0.02)
+
+    # ---- W4A4 conversion --------------------------------------------------------------
+    _QUANT_NAMES = ("to_q", "to_k", "to_v", "to_out")
+
+    @torch.no_grad()
+    def quantize_blocks(self, backend: str = "kernel", keep_oracle: bool = False):
+        """Swap the 10 linears of every block for kernel-mode QuantLinears (and enable fused
+        QKV / KV).  With keep_oracle=True also builds OracleW4A4Linear twins on the same codes,
+        selectable with set_backend("oracle")."""
+        from dsaquant_b200.kernels import vdm_w4a4 as vdm
+
+        for blk in self.blocks:
+            holders = [(blk.attn1, n) for n in self._QUANT_NAMES] + [(blk.attn2, n) for n in self._QUANT_NAMES] + \
+                      [(blk, "ffn_up"), (blk, "ffn_down")]
+            for owner, name in holders:
+                ql = _quantize_linear(getattr(owner, name))
+                setattr(owner, name, ql)
+                if keep_oracle:
+                    n, k = ql.out_features, ql.in_features
+                    codes = vdm.unpack_codes(ql.vdm_weight_packed, n, k, 2)
+                    setattr(owner, name + "_oracle", OracleW4A4Linear(ql, codes))
+                    setattr(owner, name + "_kernel", ql)
+            for attn in (blk.attn1, blk.attn2):
+                attn.use_fused_qkv_kernel = True
+                attn.qkv_kernel_backend = "vdm"
+        self.set_backend(backend)
+
+    def set_backend(self, backend: str):
+        assert backend in ("kernel", "oracle")
+        for blk in self.blocks:
+            for owner, names in ((blk.attn1, self._QUANT_NAMES), (blk.attn2, self._QUANT_NAMES),
+                                 (blk, ("ffn_up", "ffn_down"))):
+                for name in names:
+                    twin = getattr(owner, f"{name}_{backend}", None)
+                    if twin is not None:
+                        setattr(owner, name, twin)
+            for attn in (blk.attn1, blk.attn2):
+                attn.use_fused_qkv_kernel = backend == "kernel"
+        self.backend = backend
+
+    # ---- forward ------------------------------------------------------------------------
+    def embed_time(self, timestep: torch.Tensor):
+        half = self.cfg.freq_dim // 2
+        freqs = torch.pow(10000, -torch.arange(half, dtype=torch.float64, device=timestep.device) / half)
+        ang = torch.outer(timestep.double(), freqs)
+        emb = torch.cat([torch.cos(ang), torch.sin(ang)], dim=1).to(self.time_embedder[0].weight.dtype)
+        temb = self.time_embedder(emb)
+        return temb, self.time_proj(F.silu(temb)).unflatten(1, (6, -1))
+
+    @torch.no_grad()
+    def forward(self, latent: torch.Tensor, timestep: torch.Tensor, text: torch.Tensor,
+                group=None) -> torch.Tensor:
+        """latent [1,C,F,H,W], timestep [1], text [1,T,text_dim] -> noise prediction [1, L*4, out_ch]
+        (the reference's packed output layout, model.py:346-352).  With `group` set the token
+        rows are sharded over the ranks of that group and the result is gathered at the end."""
+        cfg = self.cfg
+        c1, c2, c3 = cfg.patch
+        _, c, f, h, w = latent.shape
+        fp, hp, wp = f // c1, h // c2, w // c3
+        x = latent.reshape(1, c, fp, c1, hp, c2, wp, c3).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(1, fp * hp * wp, -1)
+        m_total = x.shape[1]
+        freqs = rope_table(cfg.dim // cfg.heads, fp, hp, wp, latent.device)
+        if group is not None:
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+            s, e = sharding.row_partition(m_total, world)[rank]
+            x, freqs = x[:, s:e], freqs[s:e]
+        x = self.patch_embedding_mlp(x.to(self.patch_embedding_mlp.weight.dtype))
+        temb, temb6 = self.embed_time(timestep)
+        ctx = self.text_embedder(text.to(x.dtype))
+        for blk in self.blocks:
+            x = blk(x, ctx, temb6, freqs, group, m_total)
+        mod = self.scale_shift_table.float() + temb.float()[:, None]
+        shift, scale = mod[:, 0][None], mod[:, 1][None]
+        x = (fp32_layer_norm(x, cfg.eps) * (1 + scale) + shift).to(x.dtype)
+        x = self.proj_out(x)
+        if group is not None:
+            x = sharding.all_gather_rows(x[0].contiguous(), m_total, group)[None]
+        n = math.prod(cfg.patch)
+        return x.reshape(1, m_total, n, -1).reshape(1, m_total * n, -1)
+
+
+def build_model(cfg: WanConfig, device, seed: int = 0, backend: str = "kernel", keep_oracle: bool = False) -> WanDiT:
+    torch.manual_seed(seed)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.float16)
+    try:
+        with torch.device(device):
+            model = WanDiT(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    model.init_weights(seed)
+    model.quantize_blocks(backend, keep_oracle)
+    for m in (model.time_embedder, model.time_proj):
+        m.float()
+    return model.eval()
+
+
+def synth_inputs(cfg: WanConfig, device, seed: int = 0, negative: bool = False):
+    g = torch.Generator(device=device).manual_seed(seed)
+    latent = torch.randn((1,) + cfg.latent, generator=g, device=device).half()
+    text = torch.randn((1, cfg.text_len, cfg.text_dim), generator=g, device=device).half()
+    if negative:
+        text = torch.randn((1, cfg.text_len, cfg.text_dim), generator=g, device=device).half()
+    timestep = torch.rand(1, generator=g, device=device) * 1000.0
+    return latent, timestep, text
+
+
+@torch.no_grad()
+def cfg_step(model: WanDiT, latent, timestep, text_cond, text_uncond, guidance: float = 5.0,
+             branch_group=None, world_group=None, branch: Optional[int] = None) -> torch.Tensor:
+    """One classifier-free-guidance denoising step: noise_uncond + s * (noise_cond - noise_uncond)
+    (vdm_infer/models/wan_vdm/pipelines/text2video.py:576-609).  Single GPU: two sequential
+    forwards.  Multi GPU: `branch` in {0,1} selects which forward this rank's group computes;
+    the two predictions are exchanged with one all-gather over `world_group`."""
+    if branch is None:
+        cond = model(latent, timestep, text_cond)
+        uncond = model(latent, timestep, text_uncond)
+        return uncond + guidance * (cond - uncond)
+    mine = model(latent, timestep, text_cond if branch == 0 else text_uncond, group=branch_group)
+    world = dist.get_world_size(world_group)
+    both = torch.empty((world,) + mine.shape, dtype=mine.dtype, device=mine.device)
+    dist.all_gather_into_tensor(both, mine.contiguous(), group=world_group)
+    half = world // 2
+    cond, uncond = both[0], both[half]
+    return uncond + guidance * (cond - uncond)
