@@ -227,7 +227,18 @@ def main() -> None:
     ap.add_argument("--cpu-rows", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
+    ap.add_argument("--workload", default="linear_set",
+                    choices=["linear_set", "dit_wan21_1.3b", "dit_wan22_5b", "dit_wan21_14b"],
+                    help="linear_set (default, the headline GEMM set) or one CFG step of a harness DiT")
+    args, extra = ap.parse_known_args()
+    if args.workload.startswith("dit_"):
+        # Full-step configurations live in the harness; same launch contract, one JSON line.
+        from harness import dit_step
+
+        sys.argv = [sys.argv[0], "--model", args.workload[4:], "--steps", str(args.steps),
+                    "--warmup", str(args.warmup)] + extra
+        dit_step.main()
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return

@@ -96,7 +96,10 @@ class OracleW4A4Linear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1]).float()
-        s = (x2.abs().amax(dim=1, keepdim=True).clamp(min=1e-5) / 7) * self.clip
+        # tensor / tensor: torch turns division by a python scalar on CUDA into a multiplication
+        # by its reciprocal, which is not the pinned IEEE division.
+        seven = torch.full((), 7.0, dtype=torch.float32, device=x2.device)
+        s = (x2.abs().amax(dim=1, keepdim=True).clamp(min=1e-5) / seven) * self.clip
         q = torch.clamp(torch.round(x2 / s), -8, 7)
         prev = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = False
