@@ -52,7 +52,7 @@ WORKLOAD = "wan14b_linear_set_M32760"
 INT8_NOMINAL_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one QKV-shaped GEMM launch, scaled from the
 # ncu capture summarised in profiles/ (M=8192 case, traffic proportional to M); None if unknown.
-GEMM_DRAM_TRAFFIC_BYTES = None
+GEMM_DRAM_TRAFFIC_BYTES = int(409.7e6 * 32760 / 8192)  # 197.7 MB read + 212.0 MB written at M=8192
 
 
 def total_ops(m: int) -> float:
