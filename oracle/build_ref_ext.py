@@ -1,7 +1,7 @@
 """Builds the REFERENCE's own CUDA extension for sm_100a as a checker / same-box GPU baseline.
 
 TEST / BASELINE INFRASTRUCTURE.  Compiles vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu from the
-reference checkout where it lies (default /root/reference, override with DSAQUANT_REFERENCE)
+reference checkout where it lies (its location is taken from DSAQUANT_REFERENCE)
 with the reference's own flags (-O3 --use_fast_math -lineinfo, vdm_w4a4.py:151-162) into
 oracle/_ref/vdm_w4a4_ref_ext.so (git-ignored; no reference source is copied).  The module is a
 pybind11 torch extension: import it with oracle._ref_loader.load().  It is used only by tests

@@ -1,7 +1,7 @@
 """Regenerates tests/golden/*.npz by running the REFERENCE's own PyTorch W4A4 path.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with DSAQUANT_REFERENCE):
+Run in a container that has the reference checkout (location: DSAQUANT_REFERENCE,
+or the default in the code below):
 
     python tests/golden/make_golden.py
 
