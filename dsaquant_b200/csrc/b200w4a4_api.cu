@@ -54,6 +54,12 @@ EncodeTiledFn get_encode() {
   return g_encode;
 }
 
+template <int CG, int EPI>
+bool set_gemm_smem() {
+  return cudaFuncSetAttribute(gemm_w4a4_kernel<CG, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmCfg<CG>::SMEM_ALLOC) == cudaSuccess;
+}
+
 // Per-device one-time set-up with that device current: capability check, SM
 // count, address of the status word, shared-memory opt-in of the GEMM kernels.
 int device_state(DeviceState** out) {
@@ -79,10 +85,9 @@ int device_state(DeviceState** out) {
     }
     st.status_ptr = static_cast<int*>(p);
     if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_w4a4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GemmCfg<1>::SMEM_ALLOC) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_w4a4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GemmCfg<2>::SMEM_ALLOC) != cudaSuccess) {
+        !set_gemm_smem<1, EPI_NONE>() || !set_gemm_smem<2, EPI_NONE>() ||
+        !set_gemm_smem<1, EPI_GELU_TANH>() || !set_gemm_smem<2, EPI_GELU_TANH>() ||
+        !set_gemm_smem<1, EPI_GATE_RESIDUAL>() || !set_gemm_smem<2, EPI_GATE_RESIDUAL>()) {
       st.err = B200W4A4_ECUDA;
       return;
     }
@@ -124,10 +129,16 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64
   return r == CUDA_SUCCESS ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
-template <int CG>
+struct EpiArgs {
+  const __half* residual = nullptr;
+  const float* gate = nullptr;
+  long long gate_row_stride = 0;
+};
+
+template <int CG, int EPI = EPI_NONE>
 int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
                 const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
-                int N, int K, cudaStream_t stream) {
+                int N, int K, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
   using C = GemmCfg<CG>;
   CUtensorMap tm_a, tm_w, tm_out;
   int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, qact, static_cast<uint64_t>(K),
@@ -154,6 +165,9 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
   p.m_tiles = (M + C::BM * CG - 1) / (C::BM * CG);
   p.n_tiles = (N + C::BN - 1) / C::BN;
   p.status = st.status_ptr;
+  p.residual = epi.residual;
+  p.gate = epi.gate;
+  p.gate_row_stride = epi.gate_row_stride;
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   const int groups = st.sm_count / CG;
   const unsigned grid = static_cast<unsigned>((tiles < groups ? tiles : groups) * CG);
@@ -170,7 +184,7 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<CG>, tm_a, tm_w, tm_out, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<CG, EPI>, tm_a, tm_w, tm_out, p);
   return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
@@ -373,6 +387,104 @@ int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* 
   int rc = b200w4a4_quantize_act(x, x_dtype, qact, B200W4A4_QACT_INT8, act_scale, M, K, clip, stream);
   if (rc != B200W4A4_OK) return rc;
   return b200w4a4_gemm(qact, act_scale, w_b200, w_scale, bias, out, nullptr, M, N, K, stream);
+}
+
+// ---- fused variants ------------------------------------------------------------------
+int b200w4a4_quantize_act_fused(const void* x_f16, int prologue, const float* mod_scale,
+                                const float* mod_shift, long long mod_row_stride, float ln_eps,
+                                void* qact, float* act_scale, int M, int K, float clip,
+                                void* stream) {
+  if (x_f16 == nullptr || qact == nullptr || act_scale == nullptr) return B200W4A4_EINVAL;
+  if (M < 1 || K < 64 || (K % 64) != 0 || K > 16384) return B200W4A4_ESHAPE;
+  if (!(clip > 0.0f)) return B200W4A4_EINVAL;
+  if (!aligned16(x_f16) || !aligned16(qact)) return B200W4A4_EALIGN;
+  if (prologue == B200W4A4_PRE_NONE)
+    return b200w4a4_quantize_act(x_f16, B200W4A4_F16, qact, B200W4A4_QACT_INT8, act_scale, M, K, clip,
+                                 stream);
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PreArgs pre;
+  pre.mod_scale = mod_scale;
+  pre.mod_shift = mod_shift;
+  pre.mod_row_stride = mod_row_stride;
+  pre.ln_eps = ln_eps;
+  cudaError_t e;
+  if (prologue == B200W4A4_PRE_GELU_TANH) {
+    e = launch_quant_act_pre<PRE_GELU_TANH>(static_cast<const __half*>(x_f16), qact, act_scale, M, K,
+                                            clip, pre, s);
+  } else if (prologue == B200W4A4_PRE_LAYERNORM_MOD) {
+    if (mod_scale == nullptr || mod_shift == nullptr) return B200W4A4_EINVAL;
+    if (!aligned16(mod_scale) || !aligned16(mod_shift) || (mod_row_stride % 4) != 0)
+      return B200W4A4_EALIGN;
+    e = launch_quant_act_pre<PRE_LAYERNORM_MOD>(static_cast<const __half*>(x_f16), qact, act_scale, M,
+                                                K, clip, pre, s);
+  } else {
+    return B200W4A4_EINVAL;
+  }
+  return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+int b200w4a4_gemm_fused(const void* qact, const float* act_scale, const void* w_b200,
+                        const void* w_scale, const void* bias, void* out, int epilogue,
+                        const void* residual_f16, const float* gate, long long gate_row_stride, int M,
+                        int N, int K, void* stream) {
+  if (epilogue == B200W4A4_EPI_NONE)
+    return b200w4a4_gemm(qact, act_scale, w_b200, w_scale, bias, out, nullptr, M, N, K, stream);
+  if (qact == nullptr || act_scale == nullptr || w_b200 == nullptr || w_scale == nullptr ||
+      out == nullptr)
+    return B200W4A4_EINVAL;
+  if (M < 1) return B200W4A4_ESHAPE;
+  int rc = check_nk(N, K);
+  if (rc != B200W4A4_OK) return rc;
+  if (!aligned16(qact) || !aligned16(w_b200) || !aligned16(w_scale) || !aligned16(out) ||
+      (bias != nullptr && !aligned16(bias)))
+    return B200W4A4_EALIGN;
+  EpiArgs epi;
+  if (epilogue == B200W4A4_EPI_GATE_RESIDUAL) {
+    if (residual_f16 == nullptr || gate == nullptr) return B200W4A4_EINVAL;
+    if (!aligned16(residual_f16) || !aligned16(gate) || (gate_row_stride % 4) != 0)
+      return B200W4A4_EALIGN;
+    epi.residual = static_cast<const __half*>(residual_f16);
+    epi.gate = gate;
+    epi.gate_row_stride = gate_row_stride;
+  } else if (epilogue != B200W4A4_EPI_GELU_TANH) {
+    return B200W4A4_EINVAL;
+  }
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* ws = static_cast<const __half*>(w_scale);
+  const __half* b = static_cast<const __half*>(bias);
+  __half* o = static_cast<__half*>(out);
+  const bool pair = current_cta_group() == 2;
+  if (epilogue == B200W4A4_EPI_GELU_TANH)
+    return pair ? launch_gemm<2, EPI_GELU_TANH>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi)
+                : launch_gemm<1, EPI_GELU_TANH>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi);
+  return pair ? launch_gemm<2, EPI_GATE_RESIDUAL>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi)
+              : launch_gemm<1, EPI_GATE_RESIDUAL>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi);
+}
+
+int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,
+                          const float* mod_shift, long long mod_row_stride, float ln_eps,
+                          const void* w_b200, const void* w_scale, const void* bias, void* out,
+                          int epilogue, const void* residual_f16, const float* gate,
+                          long long gate_row_stride, void* workspace, size_t workspace_bytes, int M,
+                          int N, int K, float clip, void* stream) {
+  if (workspace == nullptr) return B200W4A4_EINVAL;
+  const size_t need = b200w4a4_linear_workspace_bytes(M, K);
+  if (need == 0) return B200W4A4_ESHAPE;
+  if (workspace_bytes < need) return B200W4A4_EWORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200W4A4_EALIGN;
+  uint8_t* wsp = static_cast<uint8_t*>(workspace);
+  float* act_scale =
+      reinterpret_cast<float*>(wsp + ((static_cast<size_t>(M) * K + 255) & ~static_cast<size_t>(255)));
+  int rc = b200w4a4_quantize_act_fused(x_f16, prologue, mod_scale, mod_shift, mod_row_stride, ln_eps,
+                                       wsp, act_scale, M, K, clip, stream);
+  if (rc != B200W4A4_OK) return rc;
+  return b200w4a4_gemm_fused(wsp, act_scale, w_b200, w_scale, bias, out, epilogue, residual_f16, gate,
+                             gate_row_stride, M, N, K, stream);
 }
 
 size_t b200w4a4_linear_noalloc_max_codes(void) { return kNoAllocCodeBytes; }

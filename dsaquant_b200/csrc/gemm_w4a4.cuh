@@ -105,6 +105,18 @@ struct GemmParams {
   int M, N, K;
   int m_tiles, n_tiles;     // in units of (CG*128) rows and 256 columns
   int* status;              // device status word
+  // epilogue extras (see the EPI_* variants)
+  const __half* residual;   // [M,N] fp16, may alias the output
+  const float* gate;        // [N] (or [M,N] with gate_row_stride = N)
+  long long gate_row_stride;
+};
+
+// Work fused behind the dequantisation (what the caller would otherwise run as separate
+// elementwise kernels over the [M,N] output).  y16 = fp16(acc * sa * sw + bias) in every case.
+enum : int {
+  EPI_NONE = 0,           // out = y16
+  EPI_GELU_TANH = 1,      // out = fp16(gelu_tanh(y16))                        FFN up projection
+  EPI_GATE_RESIDUAL = 2,  // out = fp16(float(residual) + float(y16) * gate)   attention / FFN output + skip
 };
 
 namespace detail {
@@ -191,7 +203,15 @@ struct RingPos {
   }
 };
 
-template <int CG>
+__device__ __forceinline__ float epi_gelu_tanh(float x) {
+  const float kBeta = 0.7978845608028654f;  // sqrt(2/pi)
+  const float kKappa = 0.044715f;
+  const float x3 = x * x * x;
+  const float inner = kBeta * (x + kKappa * x3);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+template <int CG, int EPI = EPI_NONE>
 __global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
@@ -490,6 +510,19 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (p.bias != nullptr) bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + 8 * g));
             const __half2* ws2 = reinterpret_cast<const __half2*>(&wsv);
             const __half2* b2 = reinterpret_cast<const __half2*>(&bv);
+            uint4 resv = make_uint4(0, 0, 0, 0);
+            float gt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if constexpr (EPI == EPI_GATE_RESIDUAL) {
+              if (row < p.M) {
+                resv = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.N + col0 + 8 * g);
+                const float* gp = p.gate + row * p.gate_row_stride + col0 + 8 * g;
+                const float4 g0 = __ldg(reinterpret_cast<const float4*>(gp));
+                const float4 g1 = __ldg(reinterpret_cast<const float4*>(gp) + 1);
+                gt[0] = g0.x; gt[1] = g0.y; gt[2] = g0.z; gt[3] = g0.w;
+                gt[4] = g1.x; gt[5] = g1.y; gt[6] = g1.z; gt[7] = g1.w;
+              }
+            }
+            const __half2* r2 = reinterpret_cast<const __half2*>(&resv);
             uint32_t packed[4];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
@@ -504,7 +537,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 v0 = __fadd_rn(v0, bf.x);
                 v1 = __fadd_rn(v1, bf.y);
               }
-              const __half2 o = __floats2half2_rn(v0, v1);
+              __half2 o = __floats2half2_rn(v0, v1);
+              if constexpr (EPI == EPI_GELU_TANH) {
+                const float2 y = __half22float2(o);
+                o = __floats2half2_rn(epi_gelu_tanh(y.x), epi_gelu_tanh(y.y));
+              } else if constexpr (EPI == EPI_GATE_RESIDUAL) {
+                const float2 y = __half22float2(o);
+                const float2 rf = __half22float2(r2[h]);
+                o = __floats2half2_rn(__fadd_rn(rf.x, __fmul_rn(y.x, gt[2 * h])),
+                                      __fadd_rn(rf.y, __fmul_rn(y.y, gt[2 * h + 1])));
+              }
               packed[h] = *reinterpret_cast<const uint32_t*>(&o);
             }
             const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + g);

@@ -31,7 +31,32 @@ enum : int {
   QOUT_NIBBLE = 1,  // u8 [M,K/2], element 2b in the low nibble, 2b+1 in the high nibble
 };
 
+// Work fused in front of the quantiser (what the caller would otherwise run as separate
+// elementwise / normalisation kernels over the same rows).
+enum : int {
+  PRE_NONE = 0,
+  PRE_GELU_TANH = 1,      // v = fp16(gelu_tanh(x))                       (FFN: between up and down projection)
+  PRE_LAYERNORM_MOD = 2,  // v = fp16(fp16(layernorm(x)) * (1 + scale[k]) + shift[k])   (block entry modulation)
+};
+
+struct PreArgs {
+  const float* mod_scale;    // [K] (or [M,K] with mod_row_stride = K)
+  const float* mod_shift;
+  long long mod_row_stride;  // 0: one vector for every row
+  float ln_eps;
+};
+
 namespace detail {
+
+// tanh-GELU evaluated in fp32 with the constants and operation order of the usual
+// "gelu(approximate='tanh')" definition, then rounded to fp16 like the tensor it replaces.
+__device__ __forceinline__ float gelu_tanh_f16(float x) {
+  const float kBeta = 0.7978845608028654f;  // sqrt(2/pi)
+  const float kKappa = 0.044715f;
+  const float x3 = x * x * x;
+  const float inner = kBeta * (x + kKappa * x3);
+  return __half2float(__float2half_rn(0.5f * x * (1.0f + tanhf(inner))));
+}
 
 // A chunk is 8 consecutive values of a row, kept in registers in its storage format.
 template <typename T>
@@ -222,6 +247,132 @@ quant_act_rows_kernel(const T* __restrict__ x, void* __restrict__ q, float* __re
   }
 }
 
+// Reduction of one value over the TPR threads that share a row (sum or max).
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, float* smem8, int sub) {
+  constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = IS_MAX ? fmaxf(v, other) : v + other;
+  }
+  if constexpr (TPR > 32) {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) smem8[warp] = v;
+    __syncthreads();
+    constexpr int WPR = TPR / 32;
+    const int w0 = sub * WPR;
+    v = smem8[w0];
+#pragma unroll
+    for (int w = 1; w < WPR; ++w) v = IS_MAX ? fmaxf(v, smem8[w0 + w]) : v + smem8[w0 + w];
+  }
+  return v;
+}
+
+// Quantiser with a fused prologue (fp16 input, int8 container).  The row stays in registers
+// across the prologue's own reductions (mean, variance) and the abs-max, so x is still read once
+// and the normalised / activated tensor is never written to memory.
+template <int TPR, int NCH, int PRE>
+__global__ void __launch_bounds__(256)
+quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
+                          float* __restrict__ scale, int M, int K, float clip, PreArgs pre) {
+  constexpr int ROWS = 256 / TPR;
+  __shared__ float red[3][8];
+  const int sub = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const long long row = static_cast<long long>(blockIdx.x) * ROWS + sub;
+  const bool row_ok = row < M;
+  const int nchunks = K >> 3;
+  const __half* xr = x + (row_ok ? row : 0) * static_cast<long long>(K);
+
+  detail::Chunk<__half> ch[NCH];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    if (row_ok && c < nchunks) ch[i].load(xr + 8 * c);
+  }
+
+  float mean = 0.0f, rstd = 1.0f;
+  if constexpr (PRE == PRE_LAYERNORM_MOD) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = t + i * TPR;
+      if (row_ok && c < nchunks) {
+        float v[8];
+        ch[i].values(v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[e];
+      }
+    }
+    mean = row_reduce<TPR, false>(sum, red[0], sub) / static_cast<float>(K);
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = t + i * TPR;
+      if (row_ok && c < nchunks) {
+        float v[8];
+        ch[i].values(v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sq += (v[e] - mean) * (v[e] - mean);
+      }
+    }
+    const float var = row_reduce<TPR, false>(sq, red[1], sub) / static_cast<float>(K);
+    rstd = rsqrtf(var + pre.ln_eps);
+  }
+
+  // The prologue's output for chunk i (values already rounded to fp16, held as fp32).
+  auto transformed = [&](int i, int c, float (&v)[8]) {
+    ch[i].values(v);
+    if constexpr (PRE == PRE_GELU_TANH) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = detail::gelu_tanh_f16(v[e]);
+    } else if constexpr (PRE == PRE_LAYERNORM_MOD) {
+      const float* ms = pre.mod_scale + row * pre.mod_row_stride + 8 * c;
+      const float* mh = pre.mod_shift + row * pre.mod_row_stride + 8 * c;
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(ms)), s1 = __ldg(reinterpret_cast<const float4*>(ms) + 1);
+      const float4 h0 = __ldg(reinterpret_cast<const float4*>(mh)), h1 = __ldg(reinterpret_cast<const float4*>(mh) + 1);
+      const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      const float sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float n16 = __half2float(__float2half_rn((v[e] - mean) * rstd));   // layer norm, cast to fp16
+        const float m = __fadd_rn(__fmul_rn(n16, __fadd_rn(1.0f, sc[e])), sh[e]);  // * (1 + scale) + shift
+        v[e] = __half2float(__float2half_rn(m));
+      }
+    }
+  };
+
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    if (row_ok && c < nchunks) {
+      float v[8];
+      transformed(i, c, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    }
+  }
+  amax = row_reduce<TPR, true>(amax, red[2], sub);
+  if (!row_ok) return;
+  const float s = detail::row_scale(amax, clip);
+  bool exact_only;
+  const float r = detail::scale_reciprocal(s, exact_only);
+  if (t == 0) scale[row] = s;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    if (c < nchunks) {
+      float v[8];
+      uint32_t codes[8];
+      transformed(i, c, v);
+      detail::chunk_codes(v, s, r, exact_only, codes);
+      detail::store_codes<QOUT_INT8>(q, static_cast<size_t>(row), K, c, codes);
+    }
+  }
+}
+
 // Rows too long to hold in registers: one CTA per row, two passes (the second
 // pass re-reads the row, which was just touched and sits in L1/L2).
 template <typename T, int QOUT>
@@ -281,6 +432,25 @@ inline cudaError_t launch_quant_act(const T* x, void* q, float* scale, int M, in
     quant_act_long_rows_kernel<T, QOUT><<<static_cast<unsigned>(M), 256, 0, stream>>>(x, q, scale, M,
                                                                                       K, clip);
 #undef B200W4A4_QLAUNCH
+  return cudaGetLastError();
+}
+
+template <int PRE>
+inline cudaError_t launch_quant_act_pre(const __half* x, void* q, float* scale, int M, int K,
+                                        float clip, const PreArgs& pre, cudaStream_t stream) {
+  const int nchunks = K / 8;
+  if (nchunks > 256 * 8) return cudaErrorInvalidValue;  // rows must fit in registers (K <= 16384)
+#define B200W4A4_QPLAUNCH(TPR, NCH)                                                             \
+  do {                                                                                           \
+    constexpr int ROWS = 256 / (TPR);                                                            \
+    const unsigned grid = static_cast<unsigned>((static_cast<long long>(M) + ROWS - 1) / ROWS);  \
+    quant_act_pre_rows_kernel<TPR, NCH, PRE><<<grid, 256, 0, stream>>>(x, q, scale, M, K, clip, pre); \
+  } while (0)
+  if (nchunks <= 32 * 8) B200W4A4_QPLAUNCH(32, 8);
+  else if (nchunks <= 64 * 8) B200W4A4_QPLAUNCH(64, 8);
+  else if (nchunks <= 128 * 8) B200W4A4_QPLAUNCH(128, 8);
+  else B200W4A4_QPLAUNCH(256, 8);
+#undef B200W4A4_QPLAUNCH
   return cudaGetLastError();
 }
 

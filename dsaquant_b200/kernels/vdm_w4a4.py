@@ -426,3 +426,98 @@ def last_device_status(device: Optional[int] = None) -> int:
     """Synchronises the device and returns (and clears) the kernels' time-out status word."""
     idx = torch.cuda.current_device() if device is None else int(device)
     return _load_ext().b200w4a4_last_device_status(idx)
+
+
+# --------------------------------------------------------------------------- fused variants
+_PROLOGUES = {None: 0, "none": 0, "gelu_tanh": 1, "layernorm_mod": 2}
+_EPILOGUES = {None: 0, "none": 0, "gelu_tanh": 1, "gate_residual": 2}
+
+
+def _f32_vec(t: torch.Tensor, width: int, rows: int, name: str):
+    """fp32 [width] (stride 0) or [rows, width] (stride = width), contiguous and 16-byte aligned."""
+    t = t.detach()
+    if t.dtype != torch.float32:
+        t = t.float()
+    t = t.reshape(-1, width) if t.numel() != width else t.reshape(1, width)
+    if t.shape[0] not in (1, rows):
+        raise ValueError(f"{name} must have {width} or {rows}x{width} elements")
+    t = t.contiguous()
+    if t.data_ptr() % 16 != 0:
+        t = t.clone()
+    return t, (0 if t.shape[0] == 1 else width)
+
+
+def linear_vdm_w4a4_fused(
+    x: torch.Tensor,
+    qweight: torch.Tensor,
+    wscales: torch.Tensor,
+    bias_half: Optional[torch.Tensor] = None,
+    clip_ratio: float = 1.0,
+    *,
+    prologue: Optional[str] = None,
+    mod_scale: Optional[torch.Tensor] = None,
+    mod_shift: Optional[torch.Tensor] = None,
+    ln_eps: float = 1e-6,
+    epilogue: Optional[str] = None,
+    residual: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """linear_vdm_w4a4 with the surrounding elementwise work of a DiT block folded in.
+
+    prologue  "layernorm_mod": x <- fp16(fp16(layer_norm(x)) * (1 + mod_scale) + mod_shift)
+              "gelu_tanh":     x <- fp16(gelu_tanh(x))
+    epilogue  "gelu_tanh":     y <- fp16(gelu_tanh(y))
+              "gate_residual": y <- fp16(residual.float() + y.float() * gate)
+    (the reference runs these as separate PyTorch ops around QuantLinear,
+    vdm_infer/models/wan_vdm/modules/dit_block.py:103-115).  x must be fp16."""
+    lib = _load_ext()
+    _require_cuda(x, "x")
+    if prologue not in _PROLOGUES or epilogue not in _EPILOGUES:
+        raise ValueError("unknown prologue / epilogue")
+    if x.dtype != torch.float16:
+        raise RuntimeError("the fused path takes fp16 activations")
+    x_2d, orig_shape = _as_2d_contiguous(x)
+    _check_linear_shapes(x_2d, qweight, wscales)
+    w_b200, w_scale = prepare_b200_weight(qweight, wscales)
+    m, k = x_2d.shape
+    n = qweight.shape[0]
+    dev = x_2d.device
+    pre, epi = _PROLOGUES[prologue], _EPILOGUES[epilogue]
+    ms = mh = None
+    m_stride = 0
+    if pre == 2:
+        if mod_scale is None or mod_shift is None:
+            raise ValueError("layernorm_mod needs mod_scale and mod_shift")
+        ms, m_stride = _f32_vec(mod_scale, k, m, "mod_scale")
+        mh, h_stride = _f32_vec(mod_shift, k, m, "mod_shift")
+        if h_stride != m_stride:
+            raise ValueError("mod_scale and mod_shift must have the same shape")
+    res = gt = None
+    g_stride = 0
+    if epi == 2:
+        if residual is None or gate is None:
+            raise ValueError("gate_residual needs residual and gate")
+        res = residual.reshape(-1, n)
+        if res.dtype != torch.float16 or res.shape[0] != m or not res.is_contiguous():
+            raise ValueError("residual must be a contiguous fp16 [M, N] tensor")
+        gt, g_stride = _f32_vec(gate, n, m, "gate")
+    b = bias_half
+    if b is not None:
+        b = b.detach().reshape(-1)
+        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
+            b = b.half().contiguous().clone()
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    if m == 0:
+        return out.view(*orig_shape, n)
+    ws_bytes = lib.b200w4a4_linear_workspace_bytes(m, k)
+    workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+    with _DeviceGuard(dev):
+        rc = lib.b200w4a4_linear_fused(
+            x_2d.data_ptr(), pre, ms.data_ptr() if ms is not None else None,
+            mh.data_ptr() if mh is not None else None, m_stride, float(ln_eps),
+            w_b200.data_ptr(), w_scale.data_ptr(), b.data_ptr() if b is not None else None,
+            out.data_ptr(), epi, res.data_ptr() if res is not None else None,
+            gt.data_ptr() if gt is not None else None, g_stride, workspace.data_ptr(), ws_bytes,
+            m, n, k, float(clip_ratio), _stream_ptr(dev))
+    _lib.check(rc, "linear_fused")
+    return out.view(*orig_shape, n)

@@ -34,6 +34,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="override the number of blocks (0 = model's own)")
     ap.add_argument("--cond-only", action="store_true")
+    ap.add_argument("--fused", action="store_true",
+                    help="fold layer norm + modulation, GELU and gated skips into the W4A4 library calls")
     args = ap.parse_args()
 
     import torch
@@ -58,6 +60,7 @@ def main() -> None:
     t0 = time.time()
     model = wan_dit.build_model(cfg, device, seed=0, backend="kernel")
     build_s = time.time() - t0
+    model.set_fused(args.fused)
     latent, timestep, text = wan_dit.synth_inputs(cfg, device, seed=1)
     _, _, text_neg = wan_dit.synth_inputs(cfg, device, seed=2, negative=True)
 
@@ -113,7 +116,8 @@ def main() -> None:
             "scaling": "strong", "dtype": "int8 linears / bf16 attention", "data": "synthetic",
             "config": {"workload": f"{cfg.name} CFG step" + (" (cond only)" if args.cond_only else ""),
                        "tokens": m, "layers": L, "dim": d, "ffn": f, "heads": cfg.heads,
-                       "parallelism": layout, "guidance": 5.0},
+                       "parallelism": layout, "guidance": 5.0,
+                       "fused_elementwise": bool(args.fused)},
             "w4a4_linear_tera_ops_per_step": forwards * per_fwd / 1e12,
             "output_finite": finite, "model_build_s": round(build_s, 1),
         }), flush=True)

@@ -175,18 +175,22 @@ class WanAttention(nn.Module):
 
     def forward(self, x, ctx, freqs, group=None, m_total=None):
         q, k, v = get_qkv_projections(self, x, ctx)
+        return self.to_out(self.core(q, k, v, ctx is None, freqs, group, m_total))
+
+    def core(self, q, k, v, is_self, freqs, group=None, m_total=None):
+        """RMSNorm across heads, RoPE, (K/V all-gather under row sharding), bf16 SDPA."""
+        dtype = q.dtype
         q, k = self.norm_q(q), self.norm_k(k)
         q, k, v = (t.unflatten(2, (self.heads, -1)) for t in (q, k, v))
         if freqs is not None:
             q, k = apply_rope(q, freqs), apply_rope(k, freqs)
-        if group is not None and ctx is None:
+        if group is not None and is_self:
             # row-sharded self-attention: every rank needs all keys and values of its branch
             k = sharding.all_gather_rows(k.reshape(k.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
             v = sharding.all_gather_rows(v.reshape(v.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
         o = F.scaled_dot_product_attention(q.transpose(1, 2).bfloat16(), k.transpose(1, 2).bfloat16(),
                                            v.transpose(1, 2).bfloat16(), dropout_p=0.0, is_causal=False)
-        o = o.transpose(1, 2).flatten(2, 3).to(x.dtype)
-        return self.to_out(o)
+        return o.transpose(1, 2).flatten(2, 3).to(dtype)
 
 
 class WanBlock(nn.Module):
@@ -201,7 +205,50 @@ class WanBlock(nn.Module):
         self.ffn_down = nn.Linear(cfg.ffn, d)
         self.scale_shift_table = nn.Parameter(torch.randn(1, 6, d) * 0.02)
 
+    fused = False   # kernel back-end only: fold norms / modulation / GELU / gated skips into the linears
+
+    def forward_fused(self, x, ctx, temb6, freqs, group=None, m_total=None):
+        """Same block with the elementwise work folded into the W4A4 library calls: layer norm +
+        modulation run inside the quantiser, GELU and `skip + out * gate` inside the GEMM epilogue."""
+        from dsaquant_b200.attention_qkv import _cat_cached
+        from dsaquant_b200.kernels.vdm_w4a4 import linear_vdm_w4a4, linear_vdm_w4a4_fused as fused
+
+        mod = (self.scale_shift_table.float() + temb6.float())          # [1 or L, 6, D]
+        shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (mod[:, i] for i in range(6))
+        a1, a2 = self.attn1, self.attn2
+        d = x.shape[-1]
+        clip = a1.to_q.kernel_clip_ratio
+        # 1. self-attention
+        _cat_cached(a1, "_vdm_qkv", (a1.to_q, a1.to_k, a1.to_v))
+        qkv = fused(x, a1._vdm_qkv_weight_packed, a1._vdm_qkv_weight_scale, a1._vdm_qkv_bias_half, clip,
+                    prologue="layernorm_mod", mod_scale=scale_msa, mod_shift=shift_msa, ln_eps=self.eps)
+        q, k, v = qkv.split(d, dim=-1)
+        o = a1.core(q, k, v, True, freqs, group, m_total)
+        x = fused(o, a1.to_out.vdm_weight_packed, a1.to_out.vdm_weight_scale_packed, a1.to_out._bias_half, clip,
+                  epilogue="gate_residual", residual=x, gate=gate_msa)
+        # 2. cross-attention (affine layer norm = modulation with scale = weight - 1, shift = bias)
+        q = fused(x, a2.to_q.vdm_weight_packed, a2.to_q.vdm_weight_scale_packed, a2.to_q._bias_half, clip,
+                  prologue="layernorm_mod", mod_scale=self.norm2.weight.float() - 1.0,
+                  mod_shift=self.norm2.bias.float(), ln_eps=self.eps)
+        _cat_cached(a2, "_vdm_kv", (a2.to_k, a2.to_v))
+        kv = linear_vdm_w4a4(ctx, a2._vdm_kv_weight_packed, a2._vdm_kv_weight_scale, None, clip,
+                             bias_half=a2._vdm_kv_bias_half)
+        k, v = kv.split(d, dim=-1)
+        o = a2.core(q, k, v, False, None)
+        if not hasattr(self, "_ones"):
+            self._ones = torch.ones(d, dtype=torch.float32, device=x.device)
+        x = fused(o, a2.to_out.vdm_weight_packed, a2.to_out.vdm_weight_scale_packed, a2.to_out._bias_half, clip,
+                  epilogue="gate_residual", residual=x, gate=self._ones)
+        # 3. feed-forward
+        h = fused(x, self.ffn_up.vdm_weight_packed, self.ffn_up.vdm_weight_scale_packed, self.ffn_up._bias_half, clip,
+                  prologue="layernorm_mod", mod_scale=c_scale, mod_shift=c_shift, ln_eps=self.eps,
+                  epilogue="gelu_tanh")
+        return fused(h, self.ffn_down.vdm_weight_packed, self.ffn_down.vdm_weight_scale_packed,
+                     self.ffn_down._bias_half, clip, epilogue="gate_residual", residual=x, gate=c_gate)
+
     def forward(self, x, ctx, temb6, freqs, group=None, m_total=None):
+        if self.fused:
+            return self.forward_fused(x, ctx, temb6, freqs, group, m_total)
         # temb6 [1 or L, 6, D] fp32; the reference materialises it per token (model.py:220-231).
         mod = self.scale_shift_table.float() + temb6.float()
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (mod[:, i][None] for i in range(6))
@@ -278,6 +325,14 @@ class WanDiT(nn.Module):
             for attn in (blk.attn1, blk.attn2):
                 attn.use_fused_qkv_kernel = backend == "kernel"
         self.backend = backend
+        if backend != "kernel":
+            self.set_fused(False)
+
+    def set_fused(self, on: bool):
+        """Fold norms / modulation / GELU / gated skips into the W4A4 calls (kernel back-end only)."""
+        assert not on or self.backend == "kernel"
+        for blk in self.blocks:
+            blk.fused = bool(on)
 
     # ---- forward ------------------------------------------------------------------------
     def embed_time(self, timestep: torch.Tensor):

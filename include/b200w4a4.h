@@ -117,6 +117,46 @@ int b200w4a4_linear(const void* x, int x_dtype, const void* w_b200, const void* 
                     const void* bias, void* out, void* workspace, size_t workspace_bytes, int M,
                     int N, int K, float clip, void* stream);
 
+/* ---- fused variants ------------------------------------------------------ */
+
+/* prologues: elementwise / normalisation work run inside the quantiser on the row it holds */
+#define B200W4A4_PRE_NONE 0
+#define B200W4A4_PRE_GELU_TANH 1      /* v = fp16(gelu_tanh(x)) */
+#define B200W4A4_PRE_LAYERNORM_MOD 2  /* v = fp16(fp16(layernorm(x)) * (1 + scale[k]) + shift[k]) */
+/* epilogues: elementwise work run inside the GEMM on y = fp16(acc*sa*sw + bias) */
+#define B200W4A4_EPI_NONE 0
+#define B200W4A4_EPI_GELU_TANH 1      /* out = fp16(gelu_tanh(y)) */
+#define B200W4A4_EPI_GATE_RESIDUAL 2  /* out = fp16(float(residual) + float(y) * gate[n]) */
+
+/* Quantiser with a fused prologue; x is fp16 [M,K], K <= 16384, codes go to the int8 container.
+ * LAYERNORM_MOD folds the block-entry modulation of the DiT block,
+ * `norm(x) * (1 + scale) + shift` (vdm_infer/models/wan_vdm/modules/dit_block.py:103, :113;
+ * layer norm without affine evaluated in fp32 and cast to fp16 as diffusers' FP32LayerNorm does),
+ * GELU_TANH the activation between the FFN projections (FeedForward "gelu-approximate",
+ * dit_block.py:53, :114), into the per-token quantisation that follows them, so the
+ * normalised / activated tensor is never written.  mod_scale / mod_shift are fp32 [K]
+ * (mod_row_stride = 0) or one vector per token (mod_row_stride = K). */
+int b200w4a4_quantize_act_fused(const void* x_f16, int prologue, const float* mod_scale,
+                                const float* mod_shift, long long mod_row_stride, float ln_eps,
+                                void* qact, float* act_scale, int M, int K, float clip,
+                                void* stream);
+
+/* GEMM with a fused epilogue.  GATE_RESIDUAL folds `hidden + out * gate`
+ * (dit_block.py:105, :115; gate fp32 [N], or per token with gate_row_stride = N; residual fp16
+ * [M,N], may be the same buffer as out), GELU_TANH the FFN activation. */
+int b200w4a4_gemm_fused(const void* qact, const float* act_scale, const void* w_b200,
+                        const void* w_scale, const void* bias, void* out, int epilogue,
+                        const void* residual_f16, const float* gate, long long gate_row_stride, int M,
+                        int N, int K, void* stream);
+
+/* b200w4a4_quantize_act_fused + b200w4a4_gemm_fused with the workspace of b200w4a4_linear. */
+int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,
+                          const float* mod_shift, long long mod_row_stride, float ln_eps,
+                          const void* w_b200, const void* w_scale, const void* bias, void* out,
+                          int epilogue, const void* residual_f16, const float* gate,
+                          long long gate_row_stride, void* workspace, size_t workspace_bytes, int M,
+                          int N, int K, float clip, void* stream);
+
 /* Same result as b200w4a4_linear, for callers that cannot allocate device memory.
  * (No counterpart in the reference, whose ops allocate their intermediates with
  * torch::empty on every call.)
