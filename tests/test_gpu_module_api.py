@@ -210,3 +210,20 @@ def test_host_pipeline_matches_direct_call(vdm):
         pipe.synchronize()
         for o, d in zip(outs, direct):
             assert torch.equal(o, d.cpu())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_runs_on_a_non_current_device(vdm):
+    """Per-device state of the library: tensors on cuda:1 while cuda:0 is current."""
+    x16, w16, b16 = make_case(61, 200, 256, 128)
+    ws = orc.weight_scale_absmax(w16)
+    qw = orc.quantize_weight(w16, ws)
+    ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)["out"]
+    assert torch.cuda.current_device() == 0
+    dev = torch.device("cuda", 1)
+    packed = torch.from_numpy(orc.pack_weight_v1(qw)).to(dev)
+    sp = torch.from_numpy(orc.pack_wscale_v1(ws, 256)).to(dev)
+    out = vdm.linear_vdm_w4a4(torch.from_numpy(x16).to(dev), packed, sp, torch.from_numpy(b16).to(dev), clip_ratio=0.95)
+    assert out.device == dev and torch.cuda.current_device() == 0
+    np.testing.assert_array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+    assert vdm.last_device_status(1) == 0
