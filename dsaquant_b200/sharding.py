@@ -18,20 +18,23 @@ ROW_ALIGN = 256  # one CTA-pair tile of the GEMM: keeps every shard but the last
 
 
 def row_partition(m: int, world: int, align: int = ROW_ALIGN) -> List[Tuple[int, int]]:
-    """Contiguous [start, end) row ranges, one per rank; every boundary except the end of the
-    matrix is a multiple of `align`; sizes differ by less than two aligned blocks; empty shards only
-    when there are fewer blocks than ranks."""
+    """Contiguous [start, end) row ranges, one per rank.  Every rank gets the same number of
+    aligned blocks, ceil(blocks / world), until the rows run out: all shards but the last
+    non-empty one have equal size, so an all-gather of equally padded shards leaves its padding
+    at the very end of the gathered buffer and the result is a plain prefix view.  The largest
+    shard is as small as any aligned split allows; trailing ranks are empty only when there are
+    fewer blocks than ranks."""
     if m < 0 or world < 1 or align < 1:
         raise ValueError("row_partition needs m >= 0, world >= 1, align >= 1")
     blocks = (m + align - 1) // align
-    base, extra = divmod(blocks, world)
-    bounds, start = [], 0
-    for r in range(world):
-        nblk = base + (1 if r < extra else 0)
-        end = min(m, start + nblk * align)
-        bounds.append((start, end))
-        start = end
-    return bounds
+    per = (blocks + world - 1) // world * align
+    return [(min(m, r * per), min(m, (r + 1) * per)) for r in range(world)]
+
+
+def shard_capacity(m: int, world: int, align: int = ROW_ALIGN) -> int:
+    """Rows of the (equal) padded shard every rank contributes to an all-gather."""
+    blocks = (m + align - 1) // align
+    return (blocks + world - 1) // world * align
 
 
 def shard_rows(x: torch.Tensor, rank: int, world: int, align: int = ROW_ALIGN) -> torch.Tensor:
@@ -40,21 +43,25 @@ def shard_rows(x: torch.Tensor, rank: int, world: int, align: int = ROW_ALIGN) -
     return x[start:end]
 
 
-def all_gather_rows(y_local: torch.Tensor, m_total: int, group=None, align: int = ROW_ALIGN) -> torch.Tensor:
+def all_gather_rows(y_local: torch.Tensor, m_total: int, group=None, align: int = ROW_ALIGN,
+                    async_op: bool = False):
     """All-gather row shards produced under row_partition into the full [m_total, N] tensor.
-    Shards are padded to the largest shard for the collective and trimmed afterwards."""
+    Full shards go into the collective as they are; only a short (last) shard is padded.  The
+    result is a prefix view of the gathered buffer: no copy on the receiving side.
+    With async_op=True returns (work, result_view); wait on `work` before reading the view."""
     world = dist.get_world_size(group)
-    bounds = row_partition(m_total, world, align)
-    max_rows = max(e - s for s, e in bounds)
+    cap = shard_capacity(m_total, world, align)
     n = y_local.shape[1]
-    padded = y_local.new_zeros((max_rows, n))
-    padded[: y_local.shape[0]].copy_(y_local)
-    gathered = y_local.new_empty((world * max_rows, n))
-    dist.all_gather_into_tensor(gathered, padded, group=group)
-    out = y_local.new_empty((m_total, n))
-    for r, (s, e) in enumerate(bounds):
-        out[s:e].copy_(gathered[r * max_rows: r * max_rows + (e - s)])
-    return out
+    if y_local.shape[0] != cap:
+        padded = y_local.new_zeros((cap, n))
+        padded[: y_local.shape[0]].copy_(y_local)
+        y_local = padded
+    elif not y_local.is_contiguous():
+        y_local = y_local.contiguous()
+    gathered = y_local.new_empty((world * cap, n))
+    work = dist.all_gather_into_tensor(gathered, y_local, group=group, async_op=async_op)
+    out = gathered[:m_total]
+    return (work, out) if async_op else out
 
 
 def linear_rows_sharded(x_local: torch.Tensor, qweight: torch.Tensor, wscales: torch.Tensor,

@@ -180,14 +180,22 @@ class WanAttention(nn.Module):
     def core(self, q, k, v, is_self, freqs, group=None, m_total=None):
         """RMSNorm across heads, RoPE, (K/V all-gather under row sharding), bf16 SDPA."""
         dtype = q.dtype
+        gather = group is not None and is_self
+        if gather:
+            # Row-sharded self-attention: every rank needs all keys and values of its branch.
+            # V needs no further processing, so its all-gather starts now and overlaps the
+            # RMSNorm / RoPE of q and k.
+            v_work, v_full = sharding.all_gather_rows(v.reshape(v.shape[1], -1).to(torch.bfloat16), m_total, group,
+                                                      async_op=True)
         q, k = self.norm_q(q), self.norm_k(k)
         q, k, v = (t.unflatten(2, (self.heads, -1)) for t in (q, k, v))
         if freqs is not None:
             q, k = apply_rope(q, freqs), apply_rope(k, freqs)
-        if group is not None and is_self:
-            # row-sharded self-attention: every rank needs all keys and values of its branch
-            k = sharding.all_gather_rows(k.reshape(k.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
-            v = sharding.all_gather_rows(v.reshape(v.shape[1], -1).contiguous(), m_total, group).view(1, m_total, self.heads, -1)
+        if gather:
+            k = sharding.all_gather_rows(k.reshape(k.shape[1], -1).to(torch.bfloat16), m_total, group)
+            k = k.view(1, m_total, self.heads, -1)
+            v_work.wait()
+            v = v_full.view(1, m_total, self.heads, -1)
         o = F.scaled_dot_product_attention(q.transpose(1, 2).bfloat16(), k.transpose(1, 2).bfloat16(),
                                            v.transpose(1, 2).bfloat16(), dropout_p=0.0, is_causal=False)
         return o.transpose(1, 2).flatten(2, 3).to(dtype)

@@ -21,12 +21,19 @@ def test_row_partition_properties(m, world):
     assert len(b) == world and b[0][0] == 0 and b[-1][1] == m
     for (s0, e0), (s1, e1) in zip(b, b[1:]):
         assert e0 == s1 and s0 <= e0
-    for s, e in b[:-1]:
-        assert e % sharding.ROW_ALIGN == 0 or e == m
+    cap = sharding.shard_capacity(m, world)
     sizes = [e - s for s, e in b]
-    assert max(sizes) - min(sizes) < 2 * sharding.ROW_ALIGN
+    assert cap % sharding.ROW_ALIGN == 0 and max(sizes, default=0) <= cap
+    nonempty = [z for z in sizes if z]
+    assert all(z == cap for z in nonempty[:-1])            # only the last non-empty shard may be short
+    assert all(s == min(m, r * cap) for r, (s, _) in enumerate(b))
+    # no aligned split has a smaller largest shard
+    blocks = -(-m // sharding.ROW_ALIGN)
+    assert cap == -(-blocks // world) * sharding.ROW_ALIGN
     if m == 32760 and world == 8:
         assert sizes[0] == 4096 and sizes[-1] == 32760 - 7 * 4096
+    if m == 27280 and world == 8:
+        assert sizes == [3584] * 7 + [27280 - 7 * 3584]
 
 
 def _oracle_linear(codes, ws, bias):
