@@ -280,6 +280,8 @@ def main() -> None:
     def step_device(gemm_events=None):
         for i, L in enumerate(layers):
             x = xs[L["k"]]
+            if gemm_events is not None:
+                gemm_events[i][2].record(stream)
             rc = lib.b200w4a4_quantize_act(x.data_ptr(), 0, qact.data_ptr(), 0, ascale.data_ptr(), m,
                                            L["k"], CLIP, sp)
             if gemm_events is not None:
@@ -303,8 +305,8 @@ def main() -> None:
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in layers] for _ in range(args.steps)]
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+            torch.cuda.Event(enable_timing=True)) for _ in layers] for _ in range(args.steps)]
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_start.record(stream)
@@ -317,8 +319,31 @@ def main() -> None:
     status = vdm.last_device_status(local_rank)
     if status != 0:
         raise RuntimeError(f"device-side time-out recorded by a kernel (role code {status})")
-    gemm_ms = [[a.elapsed_time(b) for a, b in step] for step in ev]
+    gemm_ms = [[a.elapsed_time(b) for a, b, _ in step] for step in ev]
     gemm_mean_ms = [sum(step[i] for step in gemm_ms) / args.steps for i in range(len(layers))]
+    quant_ms = [[q.elapsed_time(a) for a, _, q in step] for step in ev]
+    quant_mean_ms = [sum(step[i] for step in quant_ms) / args.steps for i in range(len(layers))]
+
+    # Library int8 x int8 GEMM (cuBLASLt through torch._int_mm) on the QKV shape: context for
+    # the roofline, measured in a short burst after the timed region.
+    lib_int8_tops = None
+    if rank == 0 and m % 8 == 0:
+        try:
+            k0, n0 = LAYERS[0][1], LAYERS[0][2]
+            a8 = torch.randint(-8, 8, (m, k0), device=device, dtype=torch.int8)
+            b8 = torch.randint(-8, 8, (n0, k0), device=device, dtype=torch.int8).t()
+            for _ in range(3):
+                torch._int_mm(a8, b8)
+            l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0.record(stream)
+            for _ in range(10):
+                torch._int_mm(a8, b8)
+            l1.record(stream)
+            torch.cuda.synchronize()
+            lib_int8_tops = 2.0 * m * k0 * n0 / (l0.elapsed_time(l1) / 10 * 1e-3) / 1e12
+            del a8, b8
+        except Exception:
+            lib_int8_tops = None
 
     t = torch.tensor([total_ms], dtype=torch.float64, device=device)
     if world > 1:
@@ -391,7 +416,13 @@ def main() -> None:
                          "peak_source": peak_src, "frac_of_nominal_int8_4500": achieved / INT8_NOMINAL_TOPS,
                          "all_gemms_achieved": gemm_all,
                          "gemm_ms": {LAYERS[i][0]: gemm_mean_ms[i] for i in range(len(LAYERS))},
-                         "traffic": GEMM_DRAM_TRAFFIC_BYTES},
+                         "traffic": GEMM_DRAM_TRAFFIC_BYTES,
+                         "library_int8_mm_tops_same_shape": lib_int8_tops},
+            "quantizer": {"bound": "hbm", "kernel": "quant_act_rows_kernel",
+                          "gb_per_s": {LAYERS[i][0]: m * (3.0 * LAYERS[i][1] + 4) / (quant_mean_ms[i] * 1e-3) / 1e9
+                                       for i in range(len(LAYERS))},
+                          "peak_gb_per_s": peaks.get("hbm_gbs"),
+                          "bytes_per_row": "2K (fp16 read) + K (int8 codes) + 4 (fp32 scale)"},
         }
         if not args.no_cpu_baseline and world == 1:
             r = cpu_reference_sample(args.cpu_rows)

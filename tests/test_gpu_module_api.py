@@ -227,3 +227,78 @@ def test_runs_on_a_non_current_device(vdm):
     assert out.device == dev and torch.cuda.current_device() == 0
     np.testing.assert_array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
     assert vdm.last_device_status(1) == 0
+
+
+def test_query_reports_sm100(vdm):
+    import ctypes
+
+    from dsaquant_b200 import _lib
+    lib = _lib.load()
+    sm, major, minor = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    assert lib.b200w4a4_query(0, ctypes.byref(sm), ctypes.byref(major), ctypes.byref(minor)) == 0
+    assert (major.value, minor.value) == (10, 0) and sm.value >= 100
+    assert lib.b200w4a4_query(99, None, None, None) == -5
+
+
+def test_cuda_graph_capture_and_replay(vdm):
+    """The library allocates nothing and never synchronises, so a linear can be captured in a
+    CUDA graph (after one eager call has done the per-device set-up) and replayed on new data."""
+    M, K, N = 333, 512, 256
+    x16, w16, b16 = make_case(71, M, K, N)
+    ws = orc.weight_scale_absmax(w16)
+    qw = orc.quantize_weight(w16, ws)
+    packed = torch.from_numpy(orc.pack_weight_v1(qw)).cuda()
+    sp = torch.from_numpy(orc.pack_wscale_v1(ws, K)).cuda()
+    bias = torch.from_numpy(b16).cuda()
+    x_static = torch.from_numpy(x16).cuda()
+    vdm.linear_vdm_w4a4(x_static, packed, sp, None, 0.95, bias_half=bias)      # warm-up: set-up + repack cache
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = vdm.linear_vdm_w4a4(x_static, packed, sp, None, 0.95, bias_half=bias)
+    for seed in (72, 73):
+        x_new, _, _ = make_case(seed, M, K, N)
+        x_static.copy_(torch.from_numpy(x_new).cuda())
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = orc.linear_w4a4(x_new, qw, ws, b16, 0.95)["out"]
+        np.testing.assert_array_equal(y_static.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+def test_concurrent_threads_and_streams(vdm):
+    """Two python threads, each on its own stream, share the library without interfering."""
+    import threading
+
+    M, K, N = 700, 1536, 384
+    cases = []
+    for seed in (81, 82):
+        x16, w16, b16 = make_case(seed, M, K, N)
+        ws = orc.weight_scale_absmax(w16)
+        qw = orc.quantize_weight(w16, ws)
+        cases.append((x16, qw, ws, b16, torch.from_numpy(orc.pack_weight_v1(qw)).cuda(),
+                      torch.from_numpy(orc.pack_wscale_v1(ws, K)).cuda()))
+    results, errors = [None, None], []
+
+    def work(i):
+        try:
+            x16, qw, ws, b16, packed, sp = cases[i]
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                x = torch.from_numpy(x16).cuda()
+                bias = torch.from_numpy(b16).cuda()
+                for _ in range(20):
+                    y = vdm.linear_vdm_w4a4(x, packed, sp, None, 0.95, bias_half=bias)
+                stream.synchronize()
+                results[i] = y.cpu().numpy()
+        except BaseException as exc:  # surfaced in the main thread
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i, (x16, qw, ws, b16, _, _) in enumerate(cases):
+        ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)["out"]
+        np.testing.assert_array_equal(results[i].view(np.uint16), ref.view(np.uint16))
