@@ -347,52 +347,61 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp == C::WARP_MMA) {
     // ===================== MMA issuer =====================
-    // One thread issues every MMA of the group, so its loop is kept to one barrier probe, four
-    // MMAs and one commit per stage.
+    // One thread issues every MMA of the group and its loop is the critical path of the kernel
+    // (measured: every instruction added here lengthens each stage by its latency).  It is
+    // therefore unrolled over the ring slots so that barrier addresses and descriptor words are
+    // loop-invariant registers, and a stage costs one barrier probe, four MMAs and one commit.
     if (lane == 0 && (CG == 1 || leader)) {
       constexpr uint32_t idesc = make_i8_idesc(C::BM * CG, C::BN);
       const uint64_t adesc0 = make_kmajor_sw128_desc(smem_base + C::OFF_MAIN);
       const uint64_t bdesc0 = make_kmajor_sw128_desc(smem_base + C::OFF_MAIN + C::A_BYTES);
-      RingPos<C::S> pos;
-      uint32_t local_tile = 0;
-      bool alive = true;
-      for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
-        const uint32_t ab = local_tile & 1;
-        const uint32_t aph = (local_tile >> 1) & 1;
-        if (!detail::wait_bar(bar_acc_free(ab), aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA)) {
-          alive = false;
-          break;
-        }
-        ptx::tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + ab * C::BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!detail::wait_bar(bar_full(pos.slot), pos.phase, abort_flag, p.status,
-                                DEV_TIMEOUT_MMA)) {
-            alive = false;
+      const uint32_t a_hi = static_cast<uint32_t>(adesc0 >> 32), b_hi = static_cast<uint32_t>(bdesc0 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(adesc0), b_lo0 = static_cast<uint32_t>(bdesc0);
+      auto commit_to = [&](uint32_t bar) {
+        if constexpr (CG == 1)
+          ptx::mma_commit(bar);
+        else
+          ptx::mma_commit_pair(bar, 0x3);
+      };
+      int tile = first_tile;
+      bool running = tile < num_tiles;
+      uint32_t local_tile = 0, phase = 0;
+      int kb = 0;
+      uint32_t tmem_d = tmem_base;
+      while (running) {
+#pragma unroll
+        for (int s = 0; s < C::S; ++s) {
+          if (!running) break;
+          if (kb == 0) {
+            const uint32_t ab = local_tile & 1;
+            if (!detail::wait_bar(bar_acc_free(ab), ((local_tile >> 1) & 1) ^ 1, abort_flag, p.status,
+                                  DEV_TIMEOUT_MMA)) {
+              running = false;
+              break;
+            }
+            tmem_d = tmem_base + ab * C::BN;
+          }
+          if (!detail::wait_bar(bar_full(s), phase, abort_flag, p.status, DEV_TIMEOUT_MMA)) {
+            running = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t off = pos.slot * (C::STAGE_BYTES >> 4);
-          const uint64_t adesc = adesc0 + off;
-          const uint64_t bdesc = bdesc0 + off;
-#pragma unroll
-          for (int k = 0; k < C::BK / 32; ++k) {
-            // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
-            ptx::mma_i8_ss<CG>(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc,
-                               (kb > 0 || k > 0) ? 1u : 0u);
+          // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
+          const uint32_t a_lo = a_lo0 + s * (C::STAGE_BYTES >> 4), b_lo = b_lo0 + s * (C::STAGE_BYTES >> 4);
+          ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kb > 0 ? 1u : 0u);
+          ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo + 2u, a_hi, b_lo + 2u, b_hi, idesc, 1u);
+          ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo + 4u, a_hi, b_lo + 4u, b_hi, idesc, 1u);
+          ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo + 6u, a_hi, b_lo + 6u, b_hi, idesc, 1u);
+          commit_to(bar_consumed(s));
+          if (++kb == kblocks) {
+            commit_to(bar_acc_full(local_tile & 1));
+            kb = 0;
+            ++local_tile;
+            tile += tile_step;
+            running = tile < num_tiles;
           }
-          if constexpr (CG == 1)
-            ptx::mma_commit(bar_consumed(pos.slot));
-          else
-            ptx::mma_commit_pair(bar_consumed(pos.slot), 0x3);
-          pos.advance();
         }
-        if (alive) {
-          if constexpr (CG == 1)
-            ptx::mma_commit(bar_acc_full(ab));
-          else
-            ptx::mma_commit_pair(bar_acc_full(ab), 0x3);
-        }
+        phase ^= 1;
       }
     }
   } else if (warp < C::WARP_EPI0) {
