@@ -145,3 +145,47 @@ def test_linear_against_reference_fixtures(vdm, cta_group, name):
         assert digest(codes) == str(g["a_codes_digest"])
         assert digest(acc) == str(g["acc_digest"])
         np.testing.assert_allclose(out[::61, ::53], g["ref_out_f32_sample"], rtol=1e-2, atol=5e-3)
+
+
+def test_c_abi_rejects_bad_arguments_without_launching(vdm):
+    """Error codes of the C ABI on a live device: nothing is launched, the status word stays clean."""
+    from dsaquant_b200 import _lib
+
+    lib = _lib.load()
+    s = torch.cuda.current_stream().cuda_stream
+    x = torch.zeros(64 * 128 + 8, dtype=torch.float16, device="cuda")
+    q = torch.zeros(64 * 128 + 16, dtype=torch.int8, device="cuda")
+    sc = torch.zeros(64, dtype=torch.float32, device="cuda")
+    w = torch.zeros(128 * 64, dtype=torch.uint8, device="cuda")
+    ws = torch.ones(128, dtype=torch.float16, device="cuda")
+    out = torch.zeros(64 * 128, dtype=torch.float16, device="cuda")
+    work = torch.zeros(lib.b200w4a4_linear_workspace_bytes(64, 128) + 256, dtype=torch.uint8, device="cuda")
+    ok = lambda: lib.b200w4a4_quantize_act(x.data_ptr(), 0, q.data_ptr(), 0, sc.data_ptr(), 64, 128, 1.0, s)
+    assert ok() == 0
+    assert lib.b200w4a4_quantize_act(x.data_ptr(), 0, q.data_ptr(), 0, sc.data_ptr(), 64, 96, 1.0, s) == -2    # K % 64
+    assert lib.b200w4a4_quantize_act(x.data_ptr(), 0, q.data_ptr(), 0, sc.data_ptr(), 0, 128, 1.0, s) == -2     # M < 1
+    assert lib.b200w4a4_quantize_act(x.data_ptr(), 7, q.data_ptr(), 0, sc.data_ptr(), 64, 128, 1.0, s) == -1    # dtype enum
+    assert lib.b200w4a4_quantize_act(x.data_ptr(), 0, q.data_ptr(), 5, sc.data_ptr(), 64, 128, 1.0, s) == -1    # container enum
+    assert lib.b200w4a4_quantize_act(x.data_ptr(), 0, q.data_ptr(), 0, sc.data_ptr(), 64, 128, 0.0, s) == -1    # clip
+    assert lib.b200w4a4_quantize_act(x.data_ptr() + 2, 0, q.data_ptr(), 0, sc.data_ptr(), 64, 128, 1.0, s) == -3  # alignment
+    gemm = lambda n, k, o=out: lib.b200w4a4_gemm(q.data_ptr(), sc.data_ptr(), w.data_ptr(), ws.data_ptr(), None,
+                                                 o.data_ptr(), None, 64, n, k, s)
+    assert gemm(128, 128) == 0
+    assert gemm(100, 128) == -2 and gemm(128, 100) == -2
+    assert lib.b200w4a4_gemm(q.data_ptr() + 1, sc.data_ptr(), w.data_ptr(), ws.data_ptr(), None, out.data_ptr(),
+                             None, 64, 128, 128, s) == -3
+    lin = lambda wsp, nbytes: lib.b200w4a4_linear(x.data_ptr(), 0, w.data_ptr(), ws.data_ptr(), None, out.data_ptr(),
+                                                  wsp, nbytes, 64, 128, 128, 1.0, s)
+    assert lin(work.data_ptr(), work.numel()) == 0
+    assert lin(work.data_ptr(), 16) == -6                       # workspace too small
+    assert lin(work.data_ptr() + 16, work.numel() - 16) == -3   # workspace not 256-byte aligned
+    assert lin(None, work.numel()) == -1
+    assert lib.b200w4a4_gemm_fused(q.data_ptr(), sc.data_ptr(), w.data_ptr(), ws.data_ptr(), None, out.data_ptr(), 2,
+                                   None, None, 0, 64, 128, 128, s) == -1   # gate_residual without operands
+    assert lib.b200w4a4_gemm_fused(q.data_ptr(), sc.data_ptr(), w.data_ptr(), ws.data_ptr(), None, out.data_ptr(), 9,
+                                   None, None, 0, 64, 128, 128, s) == -1
+    assert lib.b200w4a4_quantize_act_fused(x.data_ptr(), 2, None, None, 0, 1e-6, q.data_ptr(), sc.data_ptr(), 64, 128,
+                                           1.0, s) == -1
+    assert lib.b200w4a4_unpack_codes(w.data_ptr(), q.data_ptr(), 100, 128, 2, s) == -2   # v1 needs rows % 128 == 0
+    torch.cuda.synchronize()
+    assert lib.b200w4a4_last_device_status(torch.cuda.current_device()) == 0
