@@ -138,11 +138,12 @@ def test_packed_checkpoint_load_and_forward_on_gpu(vdm, tmp_path):
     np.testing.assert_array_equal(out[0].cpu().numpy().view(np.uint16), ref.view(np.uint16))
 
 
-@pytest.mark.parametrize("K,N", [(5120, 15360), (13824, 5120)])
-def test_full_size_properties_wan14b(vdm, K, N):
-    """M = 32760 (not a multiple of the tile): sampled rows against the oracle, a checksum of
-    checksums over every accumulator, and canary rows after the M tail."""
-    M = 32760
+@pytest.mark.parametrize("M,K,N", [(32760, 5120, 15360), (32760, 13824, 5120),      # Wan 2.1 14B
+                                   (27280, 3072, 9216), (27280, 14336, 3072),       # Wan 2.2 5B
+                                   (32760, 1536, 8960), (4095, 8960, 1536)])        # Wan 2.1 1.3B, 1/8 row shard
+def test_full_size_properties_wan_shapes(vdm, M, K, N):
+    """Full benchmark shapes (M not a multiple of the tile): sampled rows against the oracle, a
+    checksum of checksums over every accumulator, and canary rows after the M tail."""
     g = torch.Generator(device="cuda").manual_seed(K + N)
     x = torch.randn(M, K, generator=g, device="cuda", dtype=torch.float32)
     x[:, torch.randperm(K, generator=torch.Generator().manual_seed(1))[: K // 100].cuda()] *= 20.0
