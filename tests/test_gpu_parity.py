@@ -189,3 +189,20 @@ def test_c_abi_rejects_bad_arguments_without_launching(vdm):
     assert lib.b200w4a4_unpack_codes(w.data_ptr(), q.data_ptr(), 100, 128, 2, s) == -2   # v1 needs rows % 128 == 0
     torch.cuda.synchronize()
     assert lib.b200w4a4_last_device_status(torch.cuda.current_device()) == 0
+
+
+def test_random_shape_sweep_bit_exact(vdm):
+    """Seeded sweep over ragged shapes: every M, K multiple of 64, N multiple of 128, clip, bias on/off,
+    both GEMM variants; codes, accumulators and fp16 outputs must equal the oracle bit for bit."""
+    rng = np.random.default_rng(2024)
+    for i in range(36):
+        M = int(rng.integers(1, 1500))
+        K = 64 * int(rng.integers(1, 40))
+        N = 128 * int(rng.integers(1, 9))
+        clip = float(rng.choice([1.0, 0.95, 0.9, 0.5]))
+        bias = bool(rng.integers(0, 2))
+        prev = vdm.set_cta_group(1 + i % 2)
+        try:
+            _gemm_case(vdm, M, K, N, seed=3000 + i, clip=clip, bias=bias)
+        finally:
+            vdm.set_cta_group(prev)

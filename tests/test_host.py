@@ -265,3 +265,40 @@ def test_install_as_vdm_infer_aliases_modules():
         for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    """Without libb200w4a4.so (and with the JIT build disabled) nothing falls back to the CPU:
+    is_available() is False, load_error() keeps the reason and every op raises."""
+    import subprocess
+    import sys
+
+    code = r"""
+import torch
+from dsaquant_b200.kernels import vdm_w4a4 as v
+assert v.is_available() is False
+assert isinstance(v.load_error(), FileNotFoundError), repr(v.load_error())
+x = torch.zeros(4, 128); qw = torch.zeros(128, 64, dtype=torch.uint8); ws = torch.zeros(128, 2, dtype=torch.float16)
+for fn in (lambda: v.linear_vdm_w4a4(x, qw, ws), lambda: v.quantize_activation_per_token(x),
+           lambda: v.pack_weight_with_scale(torch.zeros(128, 64), torch.ones(128))):
+    try:
+        fn()
+    except FileNotFoundError:
+        pass
+    else:
+        raise SystemExit("op did not raise")
+from dsaquant_b200.quantization.quant_linear import QuantLinear
+ql = QuantLinear(torch.nn.Linear(128, 128), {"w": "lsq", "act": "dynamic"}, {"w": {}, "act": {}})
+ql.wquantizer(ql.weight.detach())
+try:
+    ql.enable_vdm_kernel_mode()
+except AssertionError as e:
+    assert "not compiled/available" in str(e)
+else:
+    raise SystemExit("enable_vdm_kernel_mode did not fail")
+print("ok")
+"""
+    env = dict(__import__("os").environ, VDM_W4A4_EXTENSIONS_DIR=str(tmp_path), B200W4A4_NO_JIT="1",
+               PYTHONPATH=str(ROOT))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=str(tmp_path))
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
