@@ -225,6 +225,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-rows", type=int, default=4096)
+    ap.add_argument("--e2e-chunk-rows", type=int, default=2048)
+    ap.add_argument("--e2e-depth", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=M_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="linear_set",
@@ -360,7 +362,7 @@ def main() -> None:
     hx = {k: v.cpu().pin_memory() for k, v in xs.items()}
     hout = [torch.empty(m, L["n"], dtype=torch.float16).pin_memory() for L in layers]
     host_layers = [HostLinearLayer(L["qweight"], L["wscales"], L["bias"]) for L in layers]
-    pipe = HostLinearPipeline(device, k_max=kmax, n_max=max(L["n"] for L in layers), chunk_rows=4096)
+    pipe = HostLinearPipeline(device, k_max=kmax, n_max=max(L["n"] for L in layers), chunk_rows=args.e2e_chunk_rows, depth=args.e2e_depth)
     groups = {}
     for i, L in enumerate(layers):
         groups.setdefault(L["k"], []).append(i)
