@@ -7,9 +7,9 @@
 //   warp 0       TMA producer: activation codes (int8 container, K-major, 128B swizzle)
 //   warp 1       owns TMEM; one lane issues tcgen05.mma kind::i8 (K=32 slices)
 //   warp 2       TMA producer: packed int4 weight tiles (two codes per byte)
-//   warps 3-10   unpack the int4 weight tile into the int8 K-major/128B-swizzle
+//   warps 3-6    unpack the int4 weight tile into the int8 K-major/128B-swizzle
 //                tile the tensor core reads (tcgen05 has no s4 kind)
-//   warps 11-14  epilogue: tcgen05.ld the int32 accumulator, dequantise with the
+//   warps 7-14   epilogue: tcgen05.ld the int32 accumulator, dequantise with the
 //                per-token x per-channel scales, add bias, fp16, TMA store
 //
 // Weight nibble convention (produced by the load-time repack, see
@@ -58,7 +58,8 @@ struct GemmCfg {
   static constexpr int SB = (CG == 1) ? 3 : 4;
   static constexpr int STAGE_BYTES = A_BYTES + BU_BYTES;
   static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16 per epilogue warp
-  static constexpr int EPI_BYTES = 4 * EPI_BUF;
+  static constexpr int EPI_WARPS = 8;             // two warps per TMEM lane quadrant, half the columns each
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF;
   static constexpr int OFF_MAIN = 0;
   static constexpr int OFF_BP = OFF_MAIN + S * STAGE_BYTES;
   static constexpr int OFF_EPI = OFF_BP + SB * BP_BYTES;
@@ -67,9 +68,9 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = OFF_BAR + 8 * NUM_BARS + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack to align the base to 1024 B
   static constexpr int WARP_A_PRODUCER = 0, WARP_MMA = 1, WARP_B_PRODUCER = 2;
-  static constexpr int WARP_UNPACK0 = 3, UNPACK_WARPS = 8, WARP_EPI0 = WARP_UNPACK0 + UNPACK_WARPS;
+  static constexpr int WARP_UNPACK0 = 3, UNPACK_WARPS = 4, WARP_EPI0 = WARP_UNPACK0 + UNPACK_WARPS;
   static constexpr int UNPACK_THREADS = 32 * UNPACK_WARPS;
-  static constexpr int THREADS = 32 * (WARP_EPI0 + 4);
+  static constexpr int THREADS = 32 * (WARP_EPI0 + EPI_WARPS);
   static constexpr int TMEM_COLS = 512;          // two 128 x 256 int32 accumulators
   static constexpr int GROUP_M = 8;              // tile rasterisation: walk 8 row-tiles per column-tile
   static_assert(BP_BYTES % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
@@ -252,7 +253,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_acc_full(b), 1);
-      ptx::mbar_init(bar_acc_free(b), 4 * CG);    // epilogue warps of every CTA in the group
+      ptx::mbar_init(bar_acc_free(b), C::EPI_WARPS * CG);  // epilogue warps of every CTA in the group
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -479,12 +480,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int row = m0 + lane;
       const float sa = (row < p.M) ? __ldg(p.act_scale + row) : 0.0f;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * C::BN;
+      // Warps e and e+4 share a lane quadrant and split the tile's columns.
+      constexpr int CHUNKS = (C::BN / 32) / (C::EPI_WARPS / 4);
+      const int c_first = ((warp - C::WARP_EPI0) >> 2) * CHUNKS;
 #pragma unroll 1
-      for (int c = 0; c < C::BN / 32; ++c) {
+      for (int c = c_first; c < c_first + CHUNKS; ++c) {
         uint32_t acc[32];
         ptx::tmem_ld_32x32(taddr + 32u * c, acc);
         ptx::tmem_ld_wait();
-        if (c == C::BN / 32 - 1) {
+        if (c == c_first + CHUNKS - 1) {
           // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
           ptx::tc_fence_before_sync();
           __syncwarp();
