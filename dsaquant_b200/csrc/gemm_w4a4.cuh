@@ -75,6 +75,7 @@ struct GemmCfg {
   static constexpr int GROUP_M = 8;              // tile rasterisation: walk 8 row-tiles per column-tile
   static_assert(BP_BYTES % 1024 == 0 && BU_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "alignment");
   static_assert((B_ROWS * 4) % UNPACK_THREADS == 0, "unpack work split");
+  static_assert(((BN / 32) / (EPI_WARPS / 4)) % 2 == 0, "the epilogue loads TMEM two chunks at a time");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
 
@@ -479,16 +480,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       ptx::tc_fence_after_sync();
       const int row = m0 + lane;
       const float sa = (row < p.M) ? __ldg(p.act_scale + row) : 0.0f;
+      const bool small_k = p.K < 16384;                   // 16 * 64 * K < 2^24
+      const float sa_eff = small_k ? sa * 0.0625f : sa;   // exact: power-of-two scaling
+      const int unshift = small_k ? 0 : 4;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ab * C::BN;
       // Warps e and e+4 share a lane quadrant and split the tile's columns.
       constexpr int CHUNKS = (C::BN / 32) / (C::EPI_WARPS / 4);
       const int c_first = ((warp - C::WARP_EPI0) >> 2) * CHUNKS;
-#pragma unroll 1
-      for (int c = c_first; c < c_first + CHUNKS; ++c) {
-        uint32_t acc[32];
-        ptx::tmem_ld_32x32(taddr + 32u * c, acc);
-        ptx::tmem_ld_wait();
-        if (c == c_first + CHUNKS - 1) {
+      // Two chunks are loaded from TMEM per step so the second load's latency hides behind the
+      // first chunk's arithmetic.
+      auto process = [&](uint32_t (&acc)[32], const int c) {
+        if (c == c_first + CHUNKS - 2) {
           // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
           ptx::tc_fence_before_sync();
           __syncwarp();
@@ -501,11 +503,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         const int col0 = n0 + 32 * c;
         const bool cols_valid = col0 < p.N;  // N is a multiple of 128: a 32-chunk is all in or all out
-        if ((c & 1) == 0) {
-          // The previous TMA store must have finished reading the staging buffer.
-          if (lane == 0) ptx::tma_store_wait_read<0>();
-          __syncwarp();
-        }
+        uint4 packed4[4];
         if (cols_valid) {
           if (p.acc_dump != nullptr && row < p.M) {
             int4* dst = reinterpret_cast<int4*>(p.acc_dump + static_cast<size_t>(row) * p.N + col0);
@@ -541,11 +539,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int h = 0; h < 4; ++h) {
               const float2 wsf = __half22float2(ws2[h]);
               const float2 bf = __half22float2(b2[h]);
-              // (acc16 >> 4) is exact: every weight byte was 16 * code.
-              const float a0 = static_cast<float>(static_cast<int>(acc[8 * g + 2 * h]) >> 4);
-              const float a1 = static_cast<float>(static_cast<int>(acc[8 * g + 2 * h + 1]) >> 4);
-              float v0 = __fmul_rn(a0, __fmul_rn(sa, wsf.x));
-              float v1 = __fmul_rn(a1, __fmul_rn(sa, wsf.y));
+              // Every weight byte was 16 * code, so the accumulator is 16 * acc.  With
+              // |16 * acc| < 2^24 the conversion to fp32 is exact and the factor moves into the
+              // scale product as an exact power of two: fl((16 acc) * fl((sa / 16) * sw)) == fl(acc * fl(sa * sw)).
+              // Longer reductions undo it with an exact arithmetic shift first.
+              const int i0 = static_cast<int>(acc[8 * g + 2 * h]), i1 = static_cast<int>(acc[8 * g + 2 * h + 1]);
+              const float a0 = static_cast<float>(i0 >> unshift);
+              const float a1 = static_cast<float>(i1 >> unshift);
+              float v0 = __fmul_rn(a0, __fmul_rn(sa_eff, wsf.x));
+              float v1 = __fmul_rn(a1, __fmul_rn(sa_eff, wsf.y));
               if (p.bias != nullptr) {
                 v0 = __fadd_rn(v0, bf.x);
                 v1 = __fadd_rn(v1, bf.y);
@@ -562,9 +564,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               }
               packed[h] = *reinterpret_cast<const uint32_t*>(&o);
             }
+            packed4[g] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        if ((c & 1) == 0) {
+          // The previous TMA store must have finished reading the staging buffer; waiting here,
+          // after the arithmetic, lets that read overlap this chunk's dequantisation.
+          if (lane == 0) ptx::tma_store_wait_read<0>();
+          __syncwarp();
+        }
+        if (cols_valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
             const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + g);
-            detail::sts128(stage + ((chunk ^ row_sw) << 4),
-                           make_uint4(packed[0], packed[1], packed[2], packed[3]));
+            detail::sts128(stage + ((chunk ^ row_sw) << 4), packed4[g]);
           }
         }
         if ((c & 1) == 1) {
@@ -575,6 +588,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ptx::tma_store_commit();
           }
         }
+      };
+#pragma unroll 1
+      for (int c = c_first; c < c_first + CHUNKS; c += 2) {
+        uint32_t acc_a[32], acc_b[32];
+        ptx::tmem_ld_32x32(taddr + 32u * c, acc_a);
+        ptx::tmem_ld_32x32(taddr + 32u * (c + 1), acc_b);
+        ptx::tmem_ld_wait();
+        process(acc_a, c);
+        process(acc_b, c + 1);
       }
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
