@@ -87,7 +87,8 @@ int device_state(DeviceState** out) {
     if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess ||
         !set_gemm_smem<1, EPI_NONE>() || !set_gemm_smem<2, EPI_NONE>() ||
         !set_gemm_smem<1, EPI_GELU_TANH>() || !set_gemm_smem<2, EPI_GELU_TANH>() ||
-        !set_gemm_smem<1, EPI_GATE_RESIDUAL>() || !set_gemm_smem<2, EPI_GATE_RESIDUAL>()) {
+        !set_gemm_smem<1, EPI_GATE_RESIDUAL>() || !set_gemm_smem<2, EPI_GATE_RESIDUAL>() ||
+        !set_gemm_smem<1, EPI_SPLIT>() || !set_gemm_smem<2, EPI_SPLIT>()) {
       st.err = B200W4A4_ECUDA;
       return;
     }
@@ -133,6 +134,10 @@ struct EpiArgs {
   const __half* residual = nullptr;
   const float* gate = nullptr;
   long long gate_row_stride = 0;
+  // EPI_SPLIT: `segments` output matrices [M, N / segments] with their own row strides (elements)
+  int segments = 0;
+  __half* seg_out[3] = {nullptr, nullptr, nullptr};
+  long long seg_ld[3] = {0, 0, 0};
 };
 
 template <int CG, int EPI = EPI_NONE>
@@ -140,7 +145,8 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
                 const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
                 int N, int K, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
   using C = GemmCfg<CG>;
-  CUtensorMap tm_a, tm_w, tm_out;
+  CUtensorMap tm_a, tm_w;
+  OutMaps tm_out;
   int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, qact, static_cast<uint64_t>(K),
                      static_cast<uint64_t>(M), static_cast<uint64_t>(K), C::BK, C::BM,
                      CU_TENSOR_MAP_SWIZZLE_128B);
@@ -149,10 +155,23 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
                  static_cast<uint64_t>(N), static_cast<uint64_t>(K / 2), C::BK / 2, C::B_ROWS,
                  CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != B200W4A4_OK) return rc;
-  rc = encode_2d(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, out, static_cast<uint64_t>(N),
-                 static_cast<uint64_t>(M), static_cast<uint64_t>(N) * 2, 64, 32,
-                 CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != B200W4A4_OK) return rc;
+  if constexpr (EPI == EPI_SPLIT) {
+    const int seg_cols = N / epi.segments;
+    for (int sg = 0; sg < 3; ++sg) {
+      const int src = sg < epi.segments ? sg : 0;  // unused slots repeat segment 0 (never addressed)
+      rc = encode_2d(&tm_out.seg[sg], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, epi.seg_out[src],
+                     static_cast<uint64_t>(seg_cols), static_cast<uint64_t>(M),
+                     static_cast<uint64_t>(epi.seg_ld[src]) * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != B200W4A4_OK) return rc;
+    }
+  } else {
+    rc = encode_2d(&tm_out.seg[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, out, static_cast<uint64_t>(N),
+                   static_cast<uint64_t>(M), static_cast<uint64_t>(N) * 2, 64, 32,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != B200W4A4_OK) return rc;
+    tm_out.seg[1] = tm_out.seg[0];
+    tm_out.seg[2] = tm_out.seg[0];
+  }
 
   GemmParams p;
   p.act_scale = act_scale;
@@ -168,6 +187,7 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
   p.residual = epi.residual;
   p.gate = epi.gate;
   p.gate_row_stride = epi.gate_row_stride;
+  p.seg_cols = (EPI == EPI_SPLIT) ? N / epi.segments : N;
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   const int groups = st.sm_count / CG;
   const unsigned grid = static_cast<unsigned>((tiles < groups ? tiles : groups) * CG);
@@ -464,6 +484,40 @@ int b200w4a4_gemm_fused(const void* qact, const float* act_scale, const void* w_
                 : launch_gemm<1, EPI_GELU_TANH>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi);
   return pair ? launch_gemm<2, EPI_GATE_RESIDUAL>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi)
               : launch_gemm<1, EPI_GATE_RESIDUAL>(*st, qact, act_scale, w_b200, ws, b, o, nullptr, M, N, K, s, epi);
+}
+
+int b200w4a4_gemm_split(const void* qact, const float* act_scale, const void* w_b200,
+                        const void* w_scale, const void* bias, void* const* outs,
+                        const long long* out_ld, int segments, int M, int N, int K, void* stream) {
+  if (qact == nullptr || act_scale == nullptr || w_b200 == nullptr || w_scale == nullptr ||
+      outs == nullptr || out_ld == nullptr)
+    return B200W4A4_EINVAL;
+  if (segments < 1 || segments > 3) return B200W4A4_EINVAL;
+  if (M < 1) return B200W4A4_ESHAPE;
+  int rc = check_nk(N, K);
+  if (rc != B200W4A4_OK) return rc;
+  if ((N % segments) != 0 || ((N / segments) % 64) != 0) return B200W4A4_ESHAPE;
+  if (!aligned16(qact) || !aligned16(w_b200) || !aligned16(w_scale) ||
+      (bias != nullptr && !aligned16(bias)))
+    return B200W4A4_EALIGN;
+  EpiArgs epi;
+  epi.segments = segments;
+  for (int sg = 0; sg < segments; ++sg) {
+    if (outs[sg] == nullptr) return B200W4A4_EINVAL;
+    if (out_ld[sg] < N / segments) return B200W4A4_ESHAPE;
+    // the tensor map wants a 16-byte aligned base and row pitch
+    if (!aligned16(outs[sg]) || (out_ld[sg] % 8) != 0) return B200W4A4_EALIGN;
+    epi.seg_out[sg] = static_cast<__half*>(outs[sg]);
+    epi.seg_ld[sg] = out_ld[sg];
+  }
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* ws = static_cast<const __half*>(w_scale);
+  const __half* b = static_cast<const __half*>(bias);
+  return current_cta_group() == 2
+             ? launch_gemm<2, EPI_SPLIT>(*st, qact, act_scale, w_b200, ws, b, nullptr, nullptr, M, N, K, s, epi)
+             : launch_gemm<1, EPI_SPLIT>(*st, qact, act_scale, w_b200, ws, b, nullptr, nullptr, M, N, K, s, epi);
 }
 
 int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,

@@ -111,6 +111,13 @@ struct GemmParams {
   const __half* residual;   // [M,N] fp16, may alias the output
   const float* gate;        // [N] (or [M,N] with gate_row_stride = N)
   long long gate_row_stride;
+  int seg_cols;             // EPI_SPLIT: width of one output segment (N / segments, a multiple of 64)
+};
+
+// Tensor maps of the output: one [M,N] matrix, or (EPI_SPLIT) up to three [M,seg_cols]
+// matrices with their own base pointers and row strides.
+struct OutMaps {
+  CUtensorMap seg[3];
 };
 
 // Work fused behind the dequantisation (what the caller would otherwise run as separate
@@ -119,6 +126,7 @@ enum : int {
   EPI_NONE = 0,           // out = y16
   EPI_GELU_TANH = 1,      // out = fp16(gelu_tanh(y16))                        FFN up projection
   EPI_GATE_RESIDUAL = 2,  // out = fp16(float(residual) + float(y16) * gate)   attention / FFN output + skip
+  EPI_SPLIT = 3,          // out_s[m, n - s*seg_cols] = y16 with s = n / seg_cols   fused QKV / KV projections
 };
 
 namespace detail {
@@ -216,7 +224,7 @@ __device__ __forceinline__ float epi_gelu_tanh(float x) {
 template <int CG, int EPI = EPI_NONE>
 __global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                 const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+                 const __grid_constant__ OutMaps tm_out, const GemmParams p) {
   using C = GemmCfg<CG>;
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles want a 1024 B aligned base.
@@ -262,7 +270,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == C::WARP_A_PRODUCER && lane == 0) {
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_w);
-    ptx::prefetch_tensormap(&tm_out);
+    ptx::prefetch_tensormap(&tm_out.seg[0]);
   }
   if (warp == C::WARP_MMA) {
     ptx::tmem_alloc<CG>(ptx::smem_u32(tmem_holder), C::TMEM_COLS);
@@ -584,7 +592,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (col0 - 32 < p.N && m0 < p.M) ptx::tma_store_2d(&tm_out, stage_buf, col0 - 32, m0);
+            const int c_store = col0 - 32;
+            if (c_store < p.N && m0 < p.M) {
+              if constexpr (EPI == EPI_SPLIT) {
+                // seg_cols is a multiple of the 64-column store box, so a box lies in one segment.
+                const int sgm = c_store / p.seg_cols;
+                ptx::tma_store_2d(&tm_out.seg[sgm], stage_buf, c_store - sgm * p.seg_cols, m0);
+              } else {
+                ptx::tma_store_2d(&tm_out.seg[0], stage_buf, c_store, m0);
+              }
+            }
             ptx::tma_store_commit();
           }
         }

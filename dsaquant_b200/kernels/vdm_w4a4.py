@@ -26,10 +26,11 @@ Behavioural notes for callers of the reference module:
 """
 from __future__ import annotations
 
+import ctypes
 import os
 import weakref
 from pathlib import Path
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -381,9 +382,11 @@ def linear_vdm_w4a4_qkv(
     w_qkv_packed: Optional[torch.Tensor] = None,
     w_qkv_scale: Optional[torch.Tensor] = None,
     qkv_bias_half: Optional[torch.Tensor] = None,
+    contiguous_outputs: bool = False,
 ):
     """One activation quantisation and one GEMM with N = 3*D; returns three views split along
-    the last dimension.  Concatenating v1 buffers along dim 0 is valid because one 128-channel
+    the last dimension (contiguous_outputs=True: three contiguous tensors written by the GEMM
+    itself, same values).  Concatenating v1 buffers along dim 0 is valid because one 128-channel
     block of the v1 layout is exactly 128 rows of the [N,K/2] view."""
     if w_qkv_packed is None or w_qkv_scale is None:
         w_qkv_packed = torch.cat([q_weight_packed, k_weight_packed, v_weight_packed], dim=0).contiguous()
@@ -396,6 +399,8 @@ def linear_vdm_w4a4_qkv(
             return b.half().contiguous() if b is not None else torch.zeros(n, dtype=torch.float16, device=device)
 
         qkv_bias_half = torch.cat([_b(q_bias), _b(k_bias), _b(v_bias)], dim=0)
+    if contiguous_outputs and n % 64 == 0:
+        return linear_vdm_w4a4_split(x, w_qkv_packed, w_qkv_scale, 3, qkv_bias_half, clip_ratio)
     qkv = linear_vdm_w4a4(x, w_qkv_packed, w_qkv_scale, bias=None, clip_ratio=clip_ratio,
                           bias_half=qkv_bias_half)
     return qkv.split(n, dim=-1)
@@ -521,3 +526,87 @@ def linear_vdm_w4a4_fused(
             m, n, k, float(clip_ratio), _stream_ptr(dev))
     _lib.check(rc, "linear_fused")
     return out.view(*orig_shape, n)
+
+
+def linear_vdm_w4a4_split(
+    x: torch.Tensor,
+    qweight: torch.Tensor,
+    wscales: torch.Tensor,
+    segments: int,
+    bias_half: Optional[torch.Tensor] = None,
+    clip_ratio: float = 1.0,
+    *,
+    prologue: Optional[str] = None,
+    mod_scale: Optional[torch.Tensor] = None,
+    mod_shift: Optional[torch.Tensor] = None,
+    ln_eps: float = 1e-6,
+    outs: Optional[Sequence[torch.Tensor]] = None,
+):
+    """Fused QKV / KV projection whose GEMM writes each of the `segments` equal column groups as
+    its own [M, N/segments] fp16 matrix (the reference returns strided views of one [M,N] matrix,
+    vdm_w4a4.py:297-298).  `outs`, when given, are the destinations: 2-D fp16 tensors of that shape
+    whose rows may be strided (e.g. this rank's rows of an all-gather buffer); otherwise new
+    contiguous tensors are returned.  Values are those of linear_vdm_w4a4(...).split(...).
+    x must be fp16 when a prologue is used."""
+    lib = _load_ext()
+    _require_cuda(x, "x")
+    if prologue not in _PROLOGUES:
+        raise ValueError("unknown prologue")
+    x_2d, orig_shape = _as_2d_contiguous(x)
+    _check_linear_shapes(x_2d, qweight, wscales)
+    w_b200, w_scale = prepare_b200_weight(qweight, wscales)
+    m, k = x_2d.shape
+    n = qweight.shape[0]
+    if segments not in (1, 2, 3) or n % segments or (n // segments) % 64:
+        raise ValueError("segments must be 1..3 and N / segments a multiple of 64")
+    seg = n // segments
+    dev = x_2d.device
+    pre = _PROLOGUES[prologue]
+    if pre != 0 and x_2d.dtype != torch.float16:
+        raise RuntimeError("the fused prologues take fp16 activations")
+    ms = mh = None
+    m_stride = 0
+    if pre == 2:
+        if mod_scale is None or mod_shift is None:
+            raise ValueError("layernorm_mod needs mod_scale and mod_shift")
+        ms, m_stride = _f32_vec(mod_scale, k, m, "mod_scale")
+        mh, h_stride = _f32_vec(mod_shift, k, m, "mod_shift")
+        if h_stride != m_stride:
+            raise ValueError("mod_scale and mod_shift must have the same shape")
+    b = bias_half
+    if b is not None:
+        b = b.detach().reshape(-1)
+        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
+            b = b.half().contiguous().clone()
+    own = outs is None
+    if own:
+        outs = [torch.empty((m, seg), dtype=torch.float16, device=dev) for _ in range(segments)]
+    else:
+        if len(outs) != segments:
+            raise ValueError("one destination per segment")
+        for o in outs:
+            if (o.dtype != torch.float16 or o.dim() != 2 or tuple(o.shape) != (m, seg) or o.device != dev
+                    or (m > 0 and o.stride(1) != 1) or (m > 1 and o.stride(0) < seg)):
+                raise ValueError("each destination must be a fp16 [M, N/segments] tensor with unit column stride")
+    if m == 0:
+        return tuple(o.view(*orig_shape, seg) for o in outs) if own else tuple(outs)
+    qact = torch.empty((m, k), dtype=torch.int8, device=dev)
+    act_scale = torch.empty((m,), dtype=torch.float32, device=dev)
+    ptrs = (ctypes.c_void_p * segments)(*[o.data_ptr() for o in outs])
+    lds = (ctypes.c_longlong * segments)(*[(o.stride(0) if m > 1 else seg) for o in outs])
+    with _DeviceGuard(dev):
+        stream = _stream_ptr(dev)
+        if pre == 0:
+            rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], qact.data_ptr(), 0,
+                                           act_scale.data_ptr(), m, k, float(clip_ratio), stream)
+        else:
+            rc = lib.b200w4a4_quantize_act_fused(
+                x_2d.data_ptr(), pre, ms.data_ptr() if ms is not None else None,
+                mh.data_ptr() if mh is not None else None, m_stride, float(ln_eps), qact.data_ptr(),
+                act_scale.data_ptr(), m, k, float(clip_ratio), stream)
+        _lib.check(rc, "quantize_act")
+        rc = lib.b200w4a4_gemm_split(qact.data_ptr(), act_scale.data_ptr(), w_b200.data_ptr(),
+                                     w_scale.data_ptr(), b.data_ptr() if b is not None else None,
+                                     ptrs, lds, segments, m, n, k, stream)
+    _lib.check(rc, "gemm_split")
+    return tuple(o.view(*orig_shape, seg) for o in outs) if own else tuple(outs)

@@ -219,7 +219,7 @@ class WanBlock(nn.Module):
         """Same block with the elementwise work folded into the W4A4 library calls: layer norm +
         modulation run inside the quantiser, GELU and `skip + out * gate` inside the GEMM epilogue."""
         from dsaquant_b200.attention_qkv import _cat_cached
-        from dsaquant_b200.kernels.vdm_w4a4 import linear_vdm_w4a4, linear_vdm_w4a4_fused as fused
+        from dsaquant_b200.kernels.vdm_w4a4 import linear_vdm_w4a4_fused as fused, linear_vdm_w4a4_split as split
 
         mod = (self.scale_shift_table.float() + temb6.float())          # [1 or L, 6, D]
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (mod[:, i] for i in range(6))
@@ -228,9 +228,8 @@ class WanBlock(nn.Module):
         clip = a1.to_q.kernel_clip_ratio
         # 1. self-attention
         _cat_cached(a1, "_vdm_qkv", (a1.to_q, a1.to_k, a1.to_v))
-        qkv = fused(x, a1._vdm_qkv_weight_packed, a1._vdm_qkv_weight_scale, a1._vdm_qkv_bias_half, clip,
-                    prologue="layernorm_mod", mod_scale=scale_msa, mod_shift=shift_msa, ln_eps=self.eps)
-        q, k, v = qkv.split(d, dim=-1)
+        q, k, v = split(x, a1._vdm_qkv_weight_packed, a1._vdm_qkv_weight_scale, 3, a1._vdm_qkv_bias_half, clip,
+                        prologue="layernorm_mod", mod_scale=scale_msa, mod_shift=shift_msa, ln_eps=self.eps)
         o = a1.core(q, k, v, True, freqs, group, m_total)
         x = fused(o, a1.to_out.vdm_weight_packed, a1.to_out.vdm_weight_scale_packed, a1.to_out._bias_half, clip,
                   epilogue="gate_residual", residual=x, gate=gate_msa)
@@ -239,9 +238,7 @@ class WanBlock(nn.Module):
                   prologue="layernorm_mod", mod_scale=self.norm2.weight.float() - 1.0,
                   mod_shift=self.norm2.bias.float(), ln_eps=self.eps)
         _cat_cached(a2, "_vdm_kv", (a2.to_k, a2.to_v))
-        kv = linear_vdm_w4a4(ctx, a2._vdm_kv_weight_packed, a2._vdm_kv_weight_scale, None, clip,
-                             bias_half=a2._vdm_kv_bias_half)
-        k, v = kv.split(d, dim=-1)
+        k, v = split(ctx, a2._vdm_kv_weight_packed, a2._vdm_kv_weight_scale, 2, a2._vdm_kv_bias_half, clip)
         o = a2.core(q, k, v, False, None)
         if not hasattr(self, "_ones"):
             self._ones = torch.ones(d, dtype=torch.float32, device=x.device)

@@ -149,6 +149,17 @@ int b200w4a4_gemm_fused(const void* qact, const float* act_scale, const void* w_
                         const void* residual_f16, const float* gate, long long gate_row_stride, int M,
                         int N, int K, void* stream);
 
+/* GEMM whose output columns go to `segments` (1..3) separate matrices: segment s holds columns
+ * [s*N/segments, (s+1)*N/segments) as a [M, N/segments] fp16 matrix at outs[s] with a row pitch
+ * of out_ld[s] elements (>= N/segments, a multiple of 8; base 16-byte aligned).  N/segments must
+ * be a multiple of 64.  This is the fused QKV / KV projection writing q, k and v as contiguous
+ * tensors - or straight into rows of a larger buffer, e.g. the slot of this rank in an
+ * all-gather buffer - where the reference returns strided views of one [M,3D] matrix
+ * (linear_vdm_w4a4_qkv, vdm_w4a4.py:297-298).  Values are those of b200w4a4_gemm. */
+int b200w4a4_gemm_split(const void* qact, const float* act_scale, const void* w_b200,
+                        const void* w_scale, const void* bias, void* const* outs,
+                        const long long* out_ld, int segments, int M, int N, int K, void* stream);
+
 /* b200w4a4_quantize_act_fused + b200w4a4_gemm_fused with the workspace of b200w4a4_linear. */
 int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,
                           const float* mod_shift, long long mod_row_stride, float ln_eps,

@@ -92,3 +92,77 @@ def test_layernorm_mod_prologue(vdm, M, K, N, per_token):
     assert (q_f != q_u).float().mean().item() < 2e-3
     assert (q_f.int() - q_u.int()).abs().max().item() <= 1
     assert torch.allclose(s_f, s_u, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M,K,D,segments", [(300, 1536, 1536, 3), (1000, 5120, 384, 3), (513, 3072, 3072, 2),
+                                           (77, 256, 64, 2), (257, 1536, 128, 1), (32760, 1536, 1536, 3)])
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_split_outputs_bit_identical(vdm, M, K, D, segments, cta_group):
+    """The split epilogue stores the same values as the one-matrix GEMM, as separate tensors."""
+    if (segments * D) % 128:
+        pytest.skip("N must be a multiple of 128")
+    N = segments * D
+    packed, sp, bias = _layer(vdm, K, N, 61)
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    x = torch.randn(M, K, generator=g, device="cuda").half()
+    prev = vdm.set_cta_group(cta_group)
+    try:
+        want = vdm.linear_vdm_w4a4(x, packed, sp, None, 0.95, bias_half=bias).split(D, dim=-1)
+        got = vdm.linear_vdm_w4a4_split(x, packed, sp, segments, bias, 0.95)
+        assert len(got) == segments
+        for a, b in zip(got, want):
+            assert a.is_contiguous() and a.shape == (M, D)
+            assert torch.equal(a, b)
+        # destinations inside larger buffers: rows at an offset, wider row pitch; the rest untouched
+        pad_rows, pitch = 40, D + 64
+        bufs = [torch.full((M + 2 * pad_rows, pitch), 7.0, dtype=torch.float16, device="cuda") for _ in range(segments)]
+        views = [bf[pad_rows:pad_rows + M, 8:8 + D] for bf in bufs]
+        vdm.linear_vdm_w4a4_split(x, packed, sp, segments, bias, 0.95, outs=views)
+        for bf, v, b in zip(bufs, views, want):
+            assert torch.equal(v, b)
+            assert (bf[:pad_rows] == 7).all() and (bf[pad_rows + M:] == 7).all()
+            assert (bf[:, :8] == 7).all() and (bf[:, 8 + D:] == 7).all()
+    finally:
+        vdm.set_cta_group(prev)
+
+
+def test_split_with_layernorm_prologue_matches_fused(vdm):
+    M, K, D = 500, 1536, 1536
+    packed, sp, bias = _layer(vdm, K, 3 * D, 67)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 2).half()
+    scale = torch.randn(K, generator=g, device="cuda") * 0.1
+    shift = torch.randn(K, generator=g, device="cuda") * 0.1
+    want = vdm.linear_vdm_w4a4_fused(x, packed, sp, bias, 0.95, prologue="layernorm_mod", mod_scale=scale,
+                                     mod_shift=shift).split(D, dim=-1)
+    got = vdm.linear_vdm_w4a4_split(x, packed, sp, 3, bias, 0.95, prologue="layernorm_mod", mod_scale=scale,
+                                    mod_shift=shift)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
+def test_split_rejects_bad_arguments(vdm):
+    from dsaquant_b200 import _lib
+    lib = _lib.load()
+    import ctypes
+    M, K, N = 64, 256, 384
+    packed, sp, _ = _layer(vdm, K, N, 71)
+    x = torch.randn(M, K, device="cuda").half()
+    with pytest.raises(ValueError):
+        vdm.linear_vdm_w4a4_split(x, packed, sp, 4)
+    with pytest.raises(ValueError):
+        vdm.linear_vdm_w4a4_split(x, packed, sp, 3, outs=[torch.empty(M, 128, device="cuda").half()] * 2)
+    packed2, sp2, _ = _layer(vdm, K, 128, 73)
+    with pytest.raises(ValueError):
+        vdm.linear_vdm_w4a4_split(x, packed2, sp2, 3)        # 128 / 3
+    # C ABI: a row pitch that is not a multiple of 8 elements, and one below the segment width
+    w_b200, w_scale = vdm.prepare_b200_weight(packed, sp)
+    qa = torch.zeros(M, K, dtype=torch.int8, device="cuda")
+    sa = torch.ones(M, dtype=torch.float32, device="cuda")
+    o = torch.empty(M, 200, dtype=torch.float16, device="cuda")
+    ptrs = (ctypes.c_void_p * 3)(o.data_ptr(), o.data_ptr(), o.data_ptr())
+    for ld, code in ((132, -3), (64, -2)):
+        lds = (ctypes.c_longlong * 3)(ld, ld, ld)
+        rc = lib.b200w4a4_gemm_split(qa.data_ptr(), sa.data_ptr(), w_b200.data_ptr(), w_scale.data_ptr(), None,
+                                     ptrs, lds, 3, M, N, K, None)
+        assert rc == code
