@@ -10,8 +10,11 @@ M video tokens, fused K/V (N = 2*D) on the text tokens.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
+from . import _lib
 from .kernels.vdm_w4a4 import linear_vdm_w4a4, linear_vdm_w4a4_qkv
 
 
@@ -62,3 +65,56 @@ def get_qkv_projections(attn, hidden_states: torch.Tensor, encoder_hidden_states
 
 
 _get_qkv_projections = get_qkv_projections  # the reference's (private) name
+
+
+def rope_cos_sin(freqs: torch.Tensor) -> torch.Tensor:
+    """complex [L, 1, head_dim/2] (or [L, head_dim/2]) rotation factors as the reference builds them
+    (modules/embedding.py:103-156) -> fp32 [L, head_dim/2, 2] = (cos, sin), what qk_norm_rope reads."""
+    f = freqs.reshape(freqs.shape[0], -1)
+    return torch.view_as_real(f.to(torch.complex64)).contiguous()
+
+
+def qk_norm_rope(x: torch.Tensor, norm_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                 eps: float, head_dim: int, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """One pass over q or k ([..., L, D] fp16, rows may be strided): RMSNorm across heads with an
+    fp16 weight, rotary embedding, cast to the attention dtype; what the reference's processor does
+    with norm_q / norm_k, apply_rotary_emb and the attention op's casts (attention.py:167-177).
+    norm_weight None: no norm; cos_sin None: no rotation.  Returns a contiguous [..., L, D] tensor."""
+    lib = _lib.load()
+    if not x.is_cuda:
+        raise RuntimeError("qk_norm_rope needs CUDA tensors")
+    if x.dtype != torch.float16:
+        raise RuntimeError("qk_norm_rope takes fp16 input")
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("out_dtype must be float16 or bfloat16")
+    d = x.shape[-1]
+    lead = tuple(x.shape[:-1])
+    x2 = x.reshape(-1, d)
+    if x2.stride(1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8) or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+    if rows == 0:
+        return out.view(*lead, d)
+    w = None
+    if norm_weight is not None:
+        w = norm_weight.detach().reshape(-1)
+        if w.dtype != torch.float16 or not w.is_contiguous() or w.data_ptr() % 16:
+            w = w.half().contiguous().clone()
+        if w.numel() != d:
+            raise ValueError("norm_weight must have D elements")
+    cs = None
+    if cos_sin is not None:
+        cs = cos_sin
+        if cs.dtype != torch.float32 or not cs.is_contiguous() or cs.data_ptr() % 16:
+            cs = cs.float().contiguous().clone()
+        if cs.numel() != rows * head_dim:
+            raise ValueError("cos_sin must be [L, head_dim/2, 2] for the L rows of x")
+    with torch.cuda.device(x.device):
+        rc = lib.b200w4a4_qk_norm_rope(
+            x2.data_ptr(), x2.stride(0) if rows > 1 else d, w.data_ptr() if w is not None else None,
+            cs.data_ptr() if cs is not None else None, float(eps), int(head_dim), out.data_ptr(),
+            0 if out_dtype == torch.float16 else 1, d, rows, d,
+            torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "qk_norm_rope")
+    return out.view(*lead, d)

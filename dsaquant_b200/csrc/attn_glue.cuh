@@ -1,0 +1,147 @@
+// Per-token work between the fused QKV projection and the attention kernel, in one pass:
+//   RMSNorm over the whole row (all heads), rotary embedding, cast to the attention dtype.
+//
+// The reference runs these as separate PyTorch ops on [L, D] tensors
+// (vdm_infer/models/wan_vdm/modules/attention.py: norm_q / norm_k :167-168 with the RMSNorm of
+// :208-216, apply_rotary_emb :131-135, and the attention op's own dtype handling), i.e. about ten
+// passes over q and k per block.  Here a row is read once, kept in registers, and written once.
+//
+// Rounding points are those of the reference ops so results agree to the last fp16 bit except
+// where a reduction-order difference moves a value across a rounding boundary:
+//   n   = fp16( float(x) * rsqrt(mean(float(x)^2) + eps) )
+//   y   = fp16( n * w )                                   (fp16 multiply)
+//   re  = fp16( y[2i]*cos - y[2i+1]*sin ),  im = fp16( y[2i]*sin + y[2i+1]*cos )   (fp32 arithmetic)
+//   out = re/im as fp16, or rounded once more to bf16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "quant_act.cuh"  // row_reduce
+
+namespace b200w4a4 {
+
+struct QkNormRopeArgs {
+  const __half* x;            // [L, D], row pitch x_ld elements
+  long long x_ld;
+  const __half* weight;       // [D] or null: no normalisation
+  const float* cos_sin;       // [L, head_dim/2, 2] (cos, sin) or null: no rotation
+  float eps;
+  int head_dim;
+  void* out;                  // [L, D], row pitch out_ld elements, fp16 or bf16
+  long long out_ld;
+  int L, D;
+};
+
+// TPR threads share a row; each holds up to NCH chunks of 8 consecutive values.
+template <int TPR, int NCH, bool OUT_BF16>
+__global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRopeArgs a) {
+  constexpr int ROWS = 256 / TPR;
+  __shared__ float red[8];
+  const int sub = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const long long row = static_cast<long long>(blockIdx.x) * ROWS + sub;
+  const bool row_ok = row < a.L;
+  const int nchunks = a.D >> 3;
+  const __half* xr = a.x + (row_ok ? row : 0) * a.x_ld;
+
+  uint4 raw[NCH];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (row_ok && c < nchunks) raw[i] = __ldcs(reinterpret_cast<const uint4*>(xr + 8 * c));
+  }
+  float r = 1.0f;
+  if (a.weight != nullptr) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+    ss = row_reduce<TPR, false>(ss, red, sub);
+    r = rsqrtf(ss / static_cast<float>(a.D) + a.eps);
+  }
+  if (!row_ok) return;
+  const float* cs_row = (a.cos_sin != nullptr) ? a.cos_sin + row * static_cast<long long>(a.head_dim) : nullptr;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = t + i * TPR;
+    if (c >= nchunks) continue;
+    const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+    __half2 y[4];
+    if (a.weight != nullptr) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.weight + 8 * c));
+      const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const __half2 n = __floats2half2_rn(__fmul_rn(f.x, r), __fmul_rn(f.y, r));
+        y[j] = __hmul2(n, w2[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j] = h[j];
+    }
+    if (cs_row != nullptr) {
+      // 8 consecutive columns = 4 rotation pairs of one head; head_dim is a multiple of 8.
+      const int j0 = (8 * c) % a.head_dim;
+      const float4 cs0 = __ldg(reinterpret_cast<const float4*>(cs_row + j0));
+      const float4 cs1 = __ldg(reinterpret_cast<const float4*>(cs_row + j0) + 1);
+      const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z};
+      const float sn[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(y[j]);
+        const float re = __fsub_rn(__fmul_rn(f.x, cc[j]), __fmul_rn(f.y, sn[j]));
+        const float im = __fadd_rn(__fmul_rn(f.x, sn[j]), __fmul_rn(f.y, cc[j]));
+        y[j] = __floats2half2_rn(re, im);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+    if constexpr (OUT_BF16) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(y[j]);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+        ow[j] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + row * a.out_ld + 8 * c;
+      *reinterpret_cast<uint4*>(dst) = o;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ow[j] = *reinterpret_cast<const uint32_t*>(&y[j]);
+      __half* dst = static_cast<__half*>(a.out) + row * a.out_ld + 8 * c;
+      *reinterpret_cast<uint4*>(dst) = o;
+    }
+  }
+}
+
+template <bool OUT_BF16>
+inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t stream) {
+  const int nchunks = a.D / 8;
+  if (nchunks > 256 * 8) return cudaErrorInvalidValue;  // a row must fit in registers (D <= 16384)
+#define B200W4A4_GLUE_LAUNCH(TPR, NCH)                                                            \
+  do {                                                                                             \
+    constexpr int ROWS = 256 / (TPR);                                                              \
+    const unsigned grid = static_cast<unsigned>((static_cast<long long>(a.L) + ROWS - 1) / ROWS);  \
+    qk_norm_rope_rows_kernel<TPR, NCH, OUT_BF16><<<grid, 256, 0, stream>>>(a);                     \
+  } while (0)
+  if (nchunks <= 32 * 4) B200W4A4_GLUE_LAUNCH(32, 4);
+  else if (nchunks <= 32 * 8) B200W4A4_GLUE_LAUNCH(32, 8);
+  else if (nchunks <= 64 * 8) B200W4A4_GLUE_LAUNCH(64, 8);
+  else if (nchunks <= 128 * 8) B200W4A4_GLUE_LAUNCH(128, 8);
+  else B200W4A4_GLUE_LAUNCH(256, 8);
+#undef B200W4A4_GLUE_LAUNCH
+  return cudaGetLastError();
+}
+
+}  // namespace b200w4a4

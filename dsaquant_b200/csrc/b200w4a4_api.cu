@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "../../include/b200w4a4.h"
+#include "attn_glue.cuh"
 #include "gemm_w4a4.cuh"
 #include "quant_act.cuh"
 #include "weight_pack.cuh"
@@ -518,6 +519,38 @@ int b200w4a4_gemm_split(const void* qact, const float* act_scale, const void* w_
   return current_cta_group() == 2
              ? launch_gemm<2, EPI_SPLIT>(*st, qact, act_scale, w_b200, ws, b, nullptr, nullptr, M, N, K, s, epi)
              : launch_gemm<1, EPI_SPLIT>(*st, qact, act_scale, w_b200, ws, b, nullptr, nullptr, M, N, K, s, epi);
+}
+
+int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_weight_f16,
+                          const float* rope_cos_sin, float eps, int head_dim, void* out, int out_dtype,
+                          long long out_ld, int L, int D, void* stream) {
+  if (x_f16 == nullptr || out == nullptr) return B200W4A4_EINVAL;
+  if (out_dtype != B200W4A4_F16 && out_dtype != B200W4A4_BF16) return B200W4A4_EINVAL;
+  if (L < 1 || D < 8 || (D % 8) != 0 || D > 16384 || x_ld < D || out_ld < D) return B200W4A4_ESHAPE;
+  if (rope_cos_sin != nullptr && (head_dim < 8 || (head_dim % 8) != 0 || (D % head_dim) != 0))
+    return B200W4A4_ESHAPE;
+  if (!aligned16(x_f16) || !aligned16(out) || (x_ld % 8) != 0 || (out_ld % 8) != 0 ||
+      (norm_weight_f16 != nullptr && !aligned16(norm_weight_f16)) ||
+      (rope_cos_sin != nullptr && !aligned16(rope_cos_sin)))
+    return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  QkNormRopeArgs a;
+  a.x = static_cast<const __half*>(x_f16);
+  a.x_ld = x_ld;
+  a.weight = static_cast<const __half*>(norm_weight_f16);
+  a.cos_sin = rope_cos_sin;
+  a.eps = eps;
+  a.head_dim = head_dim;
+  a.out = out;
+  a.out_ld = out_ld;
+  a.L = L;
+  a.D = D;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cudaError_t e = (out_dtype == B200W4A4_BF16) ? launch_qk_norm_rope<true>(a, s)
+                                                     : launch_qk_norm_rope<false>(a, s);
+  return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
 int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,

@@ -17,7 +17,7 @@ CSRC = Path(__file__).resolve().parent
 ROOT = CSRC.parent.parent
 LIB_NAME = "libb200w4a4.so"
 SOURCES = ["b200w4a4_api.cu"]
-HEADERS = ["gemm_w4a4.cuh", "quant_act.cuh", "weight_pack.cuh", "ptx.cuh"]
+HEADERS = ["gemm_w4a4.cuh", "quant_act.cuh", "weight_pack.cuh", "ptx.cuh", "attn_glue.cuh"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -474,20 +474,21 @@ def linear_vdm_w4a4_fused(
     epilogue  "gelu_tanh":     y <- fp16(gelu_tanh(y))
               "gate_residual": y <- fp16(residual.float() + y.float() * gate)
     (the reference runs these as separate PyTorch ops around QuantLinear,
-    vdm_infer/models/wan_vdm/modules/dit_block.py:103-115).  x must be fp16."""
+    vdm_infer/models/wan_vdm/modules/dit_block.py:103-115).  x must be fp16 when a prologue is
+    used; without one it may also be bf16 or fp32 (quantised from its exact values)."""
     lib = _load_ext()
     _require_cuda(x, "x")
     if prologue not in _PROLOGUES or epilogue not in _EPILOGUES:
         raise ValueError("unknown prologue / epilogue")
-    if x.dtype != torch.float16:
-        raise RuntimeError("the fused path takes fp16 activations")
+    pre, epi = _PROLOGUES[prologue], _EPILOGUES[epilogue]
+    if x.dtype != torch.float16 and pre != 0:
+        raise RuntimeError("the fused prologues take fp16 activations")
     x_2d, orig_shape = _as_2d_contiguous(x)
     _check_linear_shapes(x_2d, qweight, wscales)
     w_b200, w_scale = prepare_b200_weight(qweight, wscales)
     m, k = x_2d.shape
     n = qweight.shape[0]
     dev = x_2d.device
-    pre, epi = _PROLOGUES[prologue], _EPILOGUES[epilogue]
     ms = mh = None
     m_stride = 0
     if pre == 2:
@@ -513,6 +514,23 @@ def linear_vdm_w4a4_fused(
             b = b.half().contiguous().clone()
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     if m == 0:
+        return out.view(*orig_shape, n)
+    if x_2d.dtype != torch.float16:
+        # bf16 / fp32 activations (e.g. the attention output): quantised from their exact values,
+        # then the GEMM with the fused epilogue.
+        qact = torch.empty((m, k), dtype=torch.int8, device=dev)
+        act_scale = torch.empty((m,), dtype=torch.float32, device=dev)
+        with _DeviceGuard(dev):
+            stream = _stream_ptr(dev)
+            rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], qact.data_ptr(), 0,
+                                           act_scale.data_ptr(), m, k, float(clip_ratio), stream)
+            _lib.check(rc, "quantize_act")
+            rc = lib.b200w4a4_gemm_fused(
+                qact.data_ptr(), act_scale.data_ptr(), w_b200.data_ptr(), w_scale.data_ptr(),
+                b.data_ptr() if b is not None else None, out.data_ptr(), epi,
+                res.data_ptr() if res is not None else None,
+                gt.data_ptr() if gt is not None else None, g_stride, m, n, k, stream)
+        _lib.check(rc, "gemm_fused")
         return out.view(*orig_shape, n)
     ws_bytes = lib.b200w4a4_linear_workspace_bytes(m, k)
     workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)

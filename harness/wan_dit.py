@@ -201,6 +201,35 @@ class WanAttention(nn.Module):
         return o.transpose(1, 2).flatten(2, 3).to(dtype)
 
 
+def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
+    """`WanAttention.core` with the per-token glue in the library: RMSNorm across heads, RoPE and the
+    bf16 cast of q and k run as one pass each (dsaquant_b200.attention_qkv.qk_norm_rope), v is cast
+    in one pass, and the attention output stays bf16 (the output projection quantises it directly).
+    q, k, v: [1, L, D] fp16 as written by the split QKV epilogue."""
+    from dsaquant_b200.attention_qkv import qk_norm_rope
+
+    heads = attn.heads
+    d = q.shape[-1]
+    hd = d // heads
+    eps = attn.norm_q.eps
+    cs = None if freqs is None else torch.view_as_real(freqs).reshape(freqs.shape[0], -1)
+    gather = group is not None and is_self
+    vb = qk_norm_rope(v[0], None, None, eps, hd)
+    if gather:
+        v_work, v_full = sharding.all_gather_rows(vb, m_total, group, async_op=True)
+    qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+    kn = qk_norm_rope(k[0], attn.norm_k.weight, cs, eps, hd)
+    if gather:
+        kn = sharding.all_gather_rows(kn, m_total, group)
+        v_work.wait()
+        vb = v_full
+    lq, lk = qn.shape[0], kn.shape[0]
+    o = F.scaled_dot_product_attention(qn.view(1, lq, heads, hd).transpose(1, 2),
+                                       kn.view(1, lk, heads, hd).transpose(1, 2),
+                                       vb.view(1, lk, heads, hd).transpose(1, 2), dropout_p=0.0, is_causal=False)
+    return o.transpose(1, 2).reshape(1, lq, d)
+
+
 class WanBlock(nn.Module):
     def __init__(self, cfg: WanConfig):
         super().__init__()
@@ -230,7 +259,7 @@ class WanBlock(nn.Module):
         _cat_cached(a1, "_vdm_qkv", (a1.to_q, a1.to_k, a1.to_v))
         q, k, v = split(x, a1._vdm_qkv_weight_packed, a1._vdm_qkv_weight_scale, 3, a1._vdm_qkv_bias_half, clip,
                         prologue="layernorm_mod", mod_scale=scale_msa, mod_shift=shift_msa, ln_eps=self.eps)
-        o = a1.core(q, k, v, True, freqs, group, m_total)
+        o = _core_fused(a1, q, k, v, True, freqs, group, m_total)
         x = fused(o, a1.to_out.vdm_weight_packed, a1.to_out.vdm_weight_scale_packed, a1.to_out._bias_half, clip,
                   epilogue="gate_residual", residual=x, gate=gate_msa)
         # 2. cross-attention (affine layer norm = modulation with scale = weight - 1, shift = bias)
@@ -239,7 +268,7 @@ class WanBlock(nn.Module):
                   mod_shift=self.norm2.bias.float(), ln_eps=self.eps)
         _cat_cached(a2, "_vdm_kv", (a2.to_k, a2.to_v))
         k, v = split(ctx, a2._vdm_kv_weight_packed, a2._vdm_kv_weight_scale, 2, a2._vdm_kv_bias_half, clip)
-        o = a2.core(q, k, v, False, None)
+        o = _core_fused(a2, q, k, v, False, None)
         if not hasattr(self, "_ones"):
             self._ones = torch.ones(d, dtype=torch.float32, device=x.device)
         x = fused(o, a2.to_out.vdm_weight_packed, a2.to_out.vdm_weight_scale_packed, a2.to_out._bias_half, clip,
@@ -360,7 +389,10 @@ class WanDiT(nn.Module):
         fp, hp, wp = f // c1, h // c2, w // c3
         x = latent.reshape(1, c, fp, c1, hp, c2, wp, c3).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(1, fp * hp * wp, -1)
         m_total = x.shape[1]
-        freqs = rope_table(cfg.dim // cfg.heads, fp, hp, wp, latent.device)
+        key = (fp, hp, wp, str(latent.device))
+        if getattr(self, "_rope_key", None) != key:     # the table depends on the grid only: build it once
+            self._rope_key, self._rope = key, rope_table(cfg.dim // cfg.heads, fp, hp, wp, latent.device)
+        freqs = self._rope
         if group is not None:
             rank, world = dist.get_rank(group), dist.get_world_size(group)
             s, e = sharding.row_partition(m_total, world)[rank]

@@ -168,6 +168,20 @@ int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scal
                           long long gate_row_stride, void* workspace, size_t workspace_bytes, int M,
                           int N, int K, float clip, void* stream);
 
+/* Per-token work between the fused QKV projection and the attention kernel, in one pass over
+ * a [L,D] fp16 matrix (row pitch x_ld elements): RMSNorm across the whole row with an fp16
+ * weight (norm_q / norm_k, vdm_infer/models/wan_vdm/modules/attention.py:167-168, :208-216),
+ * rotary embedding on consecutive pairs inside each head (apply_rotary_emb, :131-135) and the
+ * cast to the attention dtype.  norm_weight_f16 NULL skips the norm; rope_cos_sin NULL skips
+ * the rotation (both NULL: a plain cast/copy).  rope_cos_sin is fp32 [L, head_dim/2, 2] =
+ * (cos, sin) per token and pair, shared by all heads.  out is fp16 or bf16 (B200W4A4_F16 /
+ * B200W4A4_BF16) [L,D] with row pitch out_ld.  D % 8 == 0, D <= 16384, head_dim % 8 == 0,
+ * pitches multiples of 8.  Intermediate roundings are those of the reference ops
+ * (fp16 after the normalisation, after the weight multiply and after the rotation). */
+int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_weight_f16,
+                          const float* rope_cos_sin, float eps, int head_dim, void* out, int out_dtype,
+                          long long out_ld, int L, int D, void* stream);
+
 /* Same result as b200w4a4_linear, for callers that cannot allocate device memory.
  * (No counterpart in the reference, whose ops allocate their intermediates with
  * torch::empty on every call.)
