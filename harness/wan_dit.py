@@ -21,6 +21,10 @@ Two linear back-ends share the same int4 weight codes:
   "kernel"  dsaquant_b200 QuantLinear in kernel mode (sm_100a library), fused QKV / KV
   "oracle"  PyTorch fake-quant with per-token dynamic activation scales in fp32 (test reference)
 
+`set_fused(True)` (kernel back-end only) routes a block through the library's fused entry points:
+layer norm + modulation and GELU inside the quantiser, GELU / gated skip / split q-k-v outputs in
+the GEMM epilogue, RMSNorm across heads + RoPE + bf16 cast of q and k in one pass (qk_norm_rope).
+
 Row sharding (multi-GPU inside one CFG branch): every per-token op runs on this rank's rows;
 self-attention all-gathers K and V of the branch group after RMSNorm + RoPE.
 """
