@@ -146,6 +146,18 @@ def _as_2d_contiguous(x: torch.Tensor) -> Tuple[torch.Tensor, Tuple[int, ...]]:
     return x2, orig_shape
 
 
+def _bias_f16(b: Optional[torch.Tensor], n: int) -> Optional[torch.Tensor]:
+    """Bias as a contiguous, 16-byte aligned fp16 [N] vector (or None)."""
+    if b is None:
+        return None
+    b = b.detach().reshape(-1)
+    if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
+        b = b.half().contiguous().clone()
+    if b.numel() != n:
+        raise ValueError("bias must have N elements")
+    return b
+
+
 def _check_linear_shapes(x_2d: torch.Tensor, qweight: torch.Tensor, wscales: torch.Tensor) -> None:
     if x_2d.shape[1] % WARP_K != 0:
         raise ValueError(f"K={x_2d.shape[1]} must be a multiple of {WARP_K}")
@@ -285,13 +297,7 @@ def linear_vdm_w4a4(
     x_2d, orig_shape = _as_2d_contiguous(x)
     _check_linear_shapes(x_2d, qweight, wscales)
     w_b200, w_scale = prepare_b200_weight(qweight, wscales)
-    b = bias_half if bias_half is not None else bias
-    if b is not None:
-        b = b.detach().reshape(-1)
-        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
-            b = b.half().contiguous().clone()
-        if b.numel() != qweight.shape[0]:
-            raise ValueError("bias must have N elements")
+    b = _bias_f16(bias_half if bias_half is not None else bias, qweight.shape[0])
     out = _linear_prepared(x_2d, w_b200, w_scale, b, clip_ratio)
     return out.view(*orig_shape, -1)
 
@@ -507,11 +513,7 @@ def linear_vdm_w4a4_fused(
         if res.dtype != torch.float16 or res.shape[0] != m or not res.is_contiguous():
             raise ValueError("residual must be a contiguous fp16 [M, N] tensor")
         gt, g_stride = _f32_vec(gate, n, m, "gate")
-    b = bias_half
-    if b is not None:
-        b = b.detach().reshape(-1)
-        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
-            b = b.half().contiguous().clone()
+    b = _bias_f16(bias_half, n)
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     if m == 0:
         return out.view(*orig_shape, n)
@@ -591,11 +593,7 @@ def linear_vdm_w4a4_split(
         mh, h_stride = _f32_vec(mod_shift, k, m, "mod_shift")
         if h_stride != m_stride:
             raise ValueError("mod_scale and mod_shift must have the same shape")
-    b = bias_half
-    if b is not None:
-        b = b.detach().reshape(-1)
-        if b.dtype != torch.float16 or not b.is_contiguous() or b.data_ptr() % 16 != 0:
-            b = b.half().contiguous().clone()
+    b = _bias_f16(bias_half, n)
     own = outs is None
     if own:
         outs = [torch.empty((m, seg), dtype=torch.float16, device=dev) for _ in range(segments)]
