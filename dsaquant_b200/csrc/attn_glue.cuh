@@ -138,6 +138,7 @@ inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t str
   if (nchunks <= 32 * 4) B200W4A4_GLUE_LAUNCH(32, 4);
   else if (nchunks <= 32 * 8) B200W4A4_GLUE_LAUNCH(32, 8);
   else if (nchunks <= 64 * 8) B200W4A4_GLUE_LAUNCH(64, 8);
+  else if (nchunks <= 128 * 5) B200W4A4_GLUE_LAUNCH(128, 5);  // D = 5120
   else if (nchunks <= 128 * 8) B200W4A4_GLUE_LAUNCH(128, 8);
   else B200W4A4_GLUE_LAUNCH(256, 8);
 #undef B200W4A4_GLUE_LAUNCH

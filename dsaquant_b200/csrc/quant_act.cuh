@@ -425,8 +425,10 @@ inline cudaError_t launch_quant_act(const T* x, void* q, float* scale, int M, in
   else if (nchunks <= 32 * 8) B200W4A4_QLAUNCH(32, 8);
   else if (nchunks <= 64 * 8) B200W4A4_QLAUNCH(64, 8);
   else if (nchunks <= 128 * 4) B200W4A4_QLAUNCH(128, 4);
+  else if (nchunks <= 128 * 5) B200W4A4_QLAUNCH(128, 5);  // K = 5120: fewer registers, one more CTA per SM
   else if (nchunks <= 128 * 8) B200W4A4_QLAUNCH(128, 8);
   else if (nchunks <= 256 * 4) B200W4A4_QLAUNCH(256, 4);
+  else if (nchunks <= 256 * 7) B200W4A4_QLAUNCH(256, 7);  // K = 13824
   else if (nchunks <= 256 * 8) B200W4A4_QLAUNCH(256, 8);
   else
     quant_act_long_rows_kernel<T, QOUT><<<static_cast<unsigned>(M), 256, 0, stream>>>(x, q, scale, M,
@@ -448,6 +450,7 @@ inline cudaError_t launch_quant_act_pre(const __half* x, void* q, float* scale, 
   } while (0)
   if (nchunks <= 32 * 8) B200W4A4_QPLAUNCH(32, 8);
   else if (nchunks <= 64 * 8) B200W4A4_QPLAUNCH(64, 8);
+  else if (nchunks <= 128 * 5) B200W4A4_QPLAUNCH(128, 5);  // K = 5120
   else if (nchunks <= 128 * 8) B200W4A4_QPLAUNCH(128, 8);
   else B200W4A4_QPLAUNCH(256, 8);
 #undef B200W4A4_QPLAUNCH
