@@ -84,6 +84,22 @@ def test_wrapper_rejects_cpu_tensors_and_bad_shapes():
         v.linear_vdm_w4a4(x, qw, ws)
     with pytest.raises(RuntimeError):
         v.pack_weight_with_scale(torch.zeros(128, 64), torch.ones(128))
+    # the fused / split entry points and the attention glue have no CPU route either
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        v.linear_vdm_w4a4_fused(x.half(), qw, ws, epilogue="gelu_tanh")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        v.linear_vdm_w4a4_split(x.half(), qw, ws, 2)
+    from dsaquant_b200 import attention_qkv as aq
+    with pytest.raises(RuntimeError, match="CUDA"):
+        aq.qk_norm_rope(torch.zeros(4, 128, dtype=torch.float16), None, None, 1e-6, 64)
+    cs = aq.rope_cos_sin(torch.polar(torch.ones(5, 1, 8), torch.arange(40.0).reshape(5, 1, 8)))
+    assert cs.shape == (5, 8, 2) and cs.dtype == torch.float32
+    assert torch.allclose(cs[..., 0], torch.cos(torch.arange(40.0).reshape(5, 8)), atol=1e-6)
+    # C ABI argument checks of the new entries come before any CUDA call
+    from dsaquant_b200 import _lib
+    lib = _lib.load()
+    assert lib.b200w4a4_gemm_split(None, None, None, None, None, None, None, 3, 1, 384, 64, None) == -1
+    assert lib.b200w4a4_qk_norm_rope(None, 128, None, None, 1e-6, 64, None, 1, 128, 4, 128, None) == -1
     with pytest.raises(ValueError, match="multiple of 64"):
         v._check_linear_shapes(torch.zeros(4, 96), qw, ws)
     with pytest.raises(ValueError, match="multiple of 128"):
