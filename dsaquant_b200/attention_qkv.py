@@ -10,7 +10,8 @@ M video tokens, fused K/V (N = 2*D) on the text tokens.
 """
 from __future__ import annotations
 
-from typing import Optional
+import ctypes
+from typing import Optional, Sequence
 
 import torch
 
@@ -118,3 +119,68 @@ def qk_norm_rope(x: torch.Tensor, norm_weight: Optional[torch.Tensor], cos_sin: 
             torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "qk_norm_rope")
     return out.view(*lead, d)
+
+
+def qk_norm_rope_push(x: torch.Tensor, norm_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                      eps: float, head_dim: int, dest_ptrs: Sequence[int], dest_ld: int, row0: int,
+                      out_dtype: torch.dtype = torch.bfloat16, *, flag_ptrs: Optional[Sequence[int]] = None,
+                      flag_index: int = 0, epoch: int = 0, ticket: Optional[torch.Tensor] = None) -> None:
+    """qk_norm_rope whose rows go to every destination in `dest_ptrs` (device addresses of
+    [>= row0 + L, D] matrices with row pitch dest_ld: this GPU's gather buffer and the peer-mapped
+    buffers of the other GPUs of the group) at row offset row0.  With flag_ptrs / ticket the kernel
+    then writes `epoch` to flag_ptrs[d] + 4 * flag_index on every destination (see wait_flags).
+    Addresses are plain integers because peer memory has no torch tensor on this rank."""
+    lib = _lib.load()
+    if not x.is_cuda or x.dtype != torch.float16:
+        raise RuntimeError("qk_norm_rope_push takes fp16 CUDA tensors")
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("out_dtype must be float16 or bfloat16")
+    if (flag_ptrs is None) != (ticket is None):
+        raise ValueError("flag_ptrs and ticket go together")
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    if x2.stride(1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8) or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    if rows == 0:
+        return
+    n = len(dest_ptrs)
+    w = None
+    if norm_weight is not None:
+        w = norm_weight.detach().reshape(-1)
+        if w.dtype != torch.float16 or not w.is_contiguous() or w.data_ptr() % 16:
+            w = w.half().contiguous().clone()
+    cs = None
+    if cos_sin is not None:
+        cs = cos_sin if (cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+                         and cos_sin.data_ptr() % 16 == 0) else cos_sin.float().contiguous().clone()
+        if cs.numel() != rows * head_dim:
+            raise ValueError("cos_sin must be [L, head_dim/2, 2] for the L rows of x")
+    outs = (ctypes.c_void_p * n)(*[int(p) for p in dest_ptrs])
+    flags = None
+    if flag_ptrs is not None:
+        if len(flag_ptrs) != n:
+            raise ValueError("one flag array per destination")
+        if ticket.dtype != torch.int32 or ticket.numel() < 1 or ticket.device != x.device:
+            raise ValueError("ticket must be an int32 tensor on x's device")
+        flags = (ctypes.c_void_p * n)(*[int(p) if p else None for p in flag_ptrs])
+    with torch.cuda.device(x.device):
+        rc = lib.b200w4a4_qk_norm_rope_push(
+            x2.data_ptr(), x2.stride(0) if rows > 1 else d, w.data_ptr() if w is not None else None,
+            cs.data_ptr() if cs is not None else None, float(eps), int(head_dim), outs, n,
+            0 if out_dtype == torch.float16 else 1, int(dest_ld), int(row0), flags, int(flag_index),
+            int(epoch) & 0xFFFFFFFF, ticket.data_ptr() if ticket is not None else None, rows, d,
+            torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "qk_norm_rope_push")
+
+
+def wait_flags(flags: torch.Tensor, epoch: int, timeout_ms: int = 1000) -> None:
+    """Enqueues the bounded wait for `flags` (int32 [n <= 32], this GPU's memory) to reach `epoch`.
+    A wait that runs out is reported by vdm_w4a4.last_device_status() == 105, not by a hang."""
+    lib = _lib.load()
+    if not flags.is_cuda or flags.dtype != torch.int32 or not flags.is_contiguous():
+        raise RuntimeError("flags must be a contiguous int32 CUDA tensor")
+    with torch.cuda.device(flags.device):
+        rc = lib.b200w4a4_wait_flags(flags.data_ptr(), flags.numel(), int(epoch) & 0xFFFFFFFF, int(timeout_ms),
+                                     torch.cuda.current_stream(flags.device).cuda_stream)
+    _lib.check(rc, "wait_flags")

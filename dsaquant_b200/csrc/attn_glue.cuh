@@ -22,6 +22,8 @@
 
 namespace b200w4a4 {
 
+constexpr int kMaxPushDestinations = 8;
+
 struct QkNormRopeArgs {
   const __half* x;            // [L, D], row pitch x_ld elements
   long long x_ld;
@@ -29,13 +31,24 @@ struct QkNormRopeArgs {
   const float* cos_sin;       // [L, head_dim/2, 2] (cos, sin) or null: no rotation
   float eps;
   int head_dim;
-  void* out;                  // [L, D], row pitch out_ld elements, fp16 or bf16
+  void* out[8];               // destinations [>= out_row0 + L, D], row pitch out_ld elements, fp16 or bf16
+  int n_out;                  // 1 = plain call; >1 = the same rows go to every destination (peer buffers)
   long long out_ld;
+  long long out_row0;         // first destination row (this rank's offset inside a gathered buffer)
+  // optional completion signal: after every store of the launch is visible system-wide,
+  // flag[d][flag_index] = epoch for each destination d
+  uint32_t* flag[8];
+  int flag_index;
+  uint32_t epoch;
+  unsigned int* ticket;       // zero-initialised counter in this GPU's memory; left at zero again
   int L, D;
 };
 
+
 // TPR threads share a row; each holds up to NCH chunks of 8 consecutive values.
-template <int TPR, int NCH, bool OUT_BF16>
+// PUSH: store to every destination and raise the completion flags; the plain instantiation
+// writes out[0] only and carries none of that code.
+template <int TPR, int NCH, bool OUT_BF16, bool PUSH>
 __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRopeArgs a) {
   constexpr int ROWS = 256 / TPR;
   __shared__ float red[8];
@@ -69,12 +82,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRope
     ss = row_reduce<TPR, false>(ss, red, sub);
     r = rsqrtf(ss / static_cast<float>(a.D) + a.eps);
   }
-  if (!row_ok) return;
   const float* cs_row = (a.cos_sin != nullptr) ? a.cos_sin + row * static_cast<long long>(a.head_dim) : nullptr;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
-    if (c >= nchunks) continue;
+    if (!row_ok || c >= nchunks) continue;
     const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
     __half2 y[4];
     if (a.weight != nullptr) {
@@ -114,18 +126,70 @@ __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRope
         const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
         ow[j] = *reinterpret_cast<const uint32_t*>(&b);
       }
-      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + row * a.out_ld + 8 * c;
-      *reinterpret_cast<uint4*>(dst) = o;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) ow[j] = *reinterpret_cast<const uint32_t*>(&y[j]);
-      __half* dst = static_cast<__half*>(a.out) + row * a.out_ld + 8 * c;
-      *reinterpret_cast<uint4*>(dst) = o;
+    }
+    // fp16 and bf16 are both two bytes wide: one element offset serves either type.
+    const long long off = (a.out_row0 + row) * a.out_ld + 8 * c;
+    if constexpr (PUSH) {
+#pragma unroll
+      for (int d = 0; d < kMaxPushDestinations; ++d)   // static indices: the pointers stay in the parameter bank
+        if (d < a.n_out) *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out[d]) + off) = o;
+    } else {
+      *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out[0]) + off) = o;
+    }
+  }
+  if (PUSH && a.ticket != nullptr) {
+    // Publish: every CTA fences its stores system-wide, then takes a ticket; the CTA that takes
+    // the last one knows (through the atomic chain) that all stores of the launch are ordered
+    // before its own flag writes.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int t_last = gridDim.x - 1;
+      if (atomicAdd(a.ticket, 1u) == t_last) {
+        *a.ticket = 0u;
+        __threadfence_system();
+#pragma unroll
+        for (int d = 0; d < kMaxPushDestinations; ++d) {
+          if (d < a.n_out && a.flag[d] != nullptr)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flag[d] + a.flag_index), "r"(a.epoch) : "memory");
+        }
+      }
     }
   }
 }
 
-template <bool OUT_BF16>
+// Consumer side of the completion signal: one thread per flag waits, for a bounded time, until
+// the flag has reached `epoch` (wrap-around safe).  A wait that runs out records
+// DEV_TIMEOUT_PEER in the status word and returns; the context stays usable.
+constexpr int DEV_TIMEOUT_PEER = 105;
+
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t epoch, unsigned long long timeout_ns,
+                                  int* status) {
+  const int i = static_cast<int>(threadIdx.x);
+  if (i >= n) return;
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+    if (static_cast<int32_t>(v - epoch) >= 0) return;
+    if ((++spins & 0xFF) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > timeout_ns) {
+        atomicCAS(status, 0, DEV_TIMEOUT_PEER);
+        return;
+      }
+    }
+  }
+}
+
+template <bool OUT_BF16, bool PUSH>
 inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t stream) {
   const int nchunks = a.D / 8;
   if (nchunks > 256 * 8) return cudaErrorInvalidValue;  // a row must fit in registers (D <= 16384)
@@ -133,7 +197,7 @@ inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t str
   do {                                                                                             \
     constexpr int ROWS = 256 / (TPR);                                                              \
     const unsigned grid = static_cast<unsigned>((static_cast<long long>(a.L) + ROWS - 1) / ROWS);  \
-    qk_norm_rope_rows_kernel<TPR, NCH, OUT_BF16><<<grid, 256, 0, stream>>>(a);                     \
+    qk_norm_rope_rows_kernel<TPR, NCH, OUT_BF16, PUSH><<<grid, 256, 0, stream>>>(a);                     \
   } while (0)
   if (nchunks <= 32 * 4) B200W4A4_GLUE_LAUNCH(32, 4);
   else if (nchunks <= 32 * 8) B200W4A4_GLUE_LAUNCH(32, 8);

@@ -521,36 +521,78 @@ int b200w4a4_gemm_split(const void* qact, const float* act_scale, const void* w_
              : launch_gemm<1, EPI_SPLIT>(*st, qact, act_scale, w_b200, ws, b, nullptr, nullptr, M, N, K, s, epi);
 }
 
-int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_weight_f16,
-                          const float* rope_cos_sin, float eps, int head_dim, void* out, int out_dtype,
-                          long long out_ld, int L, int D, void* stream) {
-  if (x_f16 == nullptr || out == nullptr) return B200W4A4_EINVAL;
+int b200w4a4_qk_norm_rope_push(const void* x_f16, long long x_ld, const void* norm_weight_f16,
+                               const float* rope_cos_sin, float eps, int head_dim, void* const* outs,
+                               int n_outs, int out_dtype, long long out_ld, long long out_row0,
+                               uint32_t* const* flags, int flag_index, uint32_t epoch,
+                               unsigned int* ticket, int L, int D, void* stream) {
+  if (x_f16 == nullptr || outs == nullptr) return B200W4A4_EINVAL;
+  if (n_outs < 1 || n_outs > kMaxPushDestinations || out_row0 < 0 || flag_index < 0)
+    return B200W4A4_EINVAL;
+  if ((flags != nullptr) != (ticket != nullptr)) return B200W4A4_EINVAL;
   if (out_dtype != B200W4A4_F16 && out_dtype != B200W4A4_BF16) return B200W4A4_EINVAL;
   if (L < 1 || D < 8 || (D % 8) != 0 || D > 16384 || x_ld < D || out_ld < D) return B200W4A4_ESHAPE;
   if (rope_cos_sin != nullptr && (head_dim < 8 || (head_dim % 8) != 0 || (D % head_dim) != 0))
     return B200W4A4_ESHAPE;
-  if (!aligned16(x_f16) || !aligned16(out) || (x_ld % 8) != 0 || (out_ld % 8) != 0 ||
+  if (!aligned16(x_f16) || (x_ld % 8) != 0 || (out_ld % 8) != 0 ||
       (norm_weight_f16 != nullptr && !aligned16(norm_weight_f16)) ||
       (rope_cos_sin != nullptr && !aligned16(rope_cos_sin)))
     return B200W4A4_EALIGN;
+  QkNormRopeArgs a;
+  for (int d = 0; d < kMaxPushDestinations; ++d) {
+    a.out[d] = nullptr;
+    a.flag[d] = nullptr;
+  }
+  for (int d = 0; d < n_outs; ++d) {
+    if (outs[d] == nullptr) return B200W4A4_EINVAL;
+    if (!aligned16(outs[d])) return B200W4A4_EALIGN;
+    a.out[d] = outs[d];
+    if (flags != nullptr) a.flag[d] = flags[d];  // a null entry: no signal for that destination
+  }
   DeviceState* st = nullptr;
   const int rc = device_state(&st);
   if (rc != B200W4A4_OK) return rc;
-  QkNormRopeArgs a;
   a.x = static_cast<const __half*>(x_f16);
   a.x_ld = x_ld;
   a.weight = static_cast<const __half*>(norm_weight_f16);
   a.cos_sin = rope_cos_sin;
   a.eps = eps;
   a.head_dim = head_dim;
-  a.out = out;
+  a.n_out = n_outs;
   a.out_ld = out_ld;
+  a.out_row0 = out_row0;
+  a.flag_index = flag_index;
+  a.epoch = epoch;
+  a.ticket = ticket;
   a.L = L;
   a.D = D;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const cudaError_t e = (out_dtype == B200W4A4_BF16) ? launch_qk_norm_rope<true>(a, s)
-                                                     : launch_qk_norm_rope<false>(a, s);
+  const bool push = n_outs > 1 || ticket != nullptr;
+  cudaError_t e;
+  if (out_dtype == B200W4A4_BF16)
+    e = push ? launch_qk_norm_rope<true, true>(a, s) : launch_qk_norm_rope<true, false>(a, s);
+  else
+    e = push ? launch_qk_norm_rope<false, true>(a, s) : launch_qk_norm_rope<false, false>(a, s);
   return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_weight_f16,
+                          const float* rope_cos_sin, float eps, int head_dim, void* out, int out_dtype,
+                          long long out_ld, int L, int D, void* stream) {
+  if (out == nullptr) return B200W4A4_EINVAL;
+  void* outs[1] = {out};
+  return b200w4a4_qk_norm_rope_push(x_f16, x_ld, norm_weight_f16, rope_cos_sin, eps, head_dim, outs, 1,
+                                    out_dtype, out_ld, 0, nullptr, 0, 0u, nullptr, L, D, stream);
+}
+
+int b200w4a4_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int timeout_ms, void* stream) {
+  if (flags == nullptr || n < 1 || n > 32 || timeout_ms < 1 || timeout_ms > 10000) return B200W4A4_EINVAL;
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      flags, n, epoch, static_cast<unsigned long long>(timeout_ms) * 1000000ull, st->status_ptr);
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
 int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,

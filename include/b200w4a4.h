@@ -182,6 +182,27 @@ int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_we
                           const float* rope_cos_sin, float eps, int head_dim, void* out, int out_dtype,
                           long long out_ld, int L, int D, void* stream);
 
+/* b200w4a4_qk_norm_rope whose result goes to n_outs (1..8) destination matrices at row offset
+ * out_row0 - e.g. this rank's rows of the gathered K (or V) buffer of every GPU of a row-sharded
+ * attention group, the peers' buffers being peer-mapped memory: plain stores, the all-gather
+ * happens inside the producing kernel.  All destinations share dtype and row pitch.
+ * flags / ticket (both or neither): when every store of the launch is visible system-wide, the
+ * kernel writes `epoch` to flags[d][flag_index] for each destination d with a non-NULL flags[d]
+ * (release, system scope).  flags[d] points into the memory of the GPU that owns destination d;
+ * ticket is a zero-initialised unsigned int in this GPU's memory, zero again when the kernel ends.
+ * The consumer calls b200w4a4_wait_flags on its own flag array before it reads the buffer. */
+int b200w4a4_qk_norm_rope_push(const void* x_f16, long long x_ld, const void* norm_weight_f16,
+                               const float* rope_cos_sin, float eps, int head_dim, void* const* outs,
+                               int n_outs, int out_dtype, long long out_ld, long long out_row0,
+                               uint32_t* const* flags, int flag_index, uint32_t epoch,
+                               unsigned int* ticket, int L, int D, void* stream);
+
+/* Enqueues a one-warp kernel that waits until flags[i] has reached `epoch` (wrap-around safe
+ * comparison) for every i < n (n <= 32), for at most timeout_ms (1..10000).  A wait that runs out
+ * records code 105 in the device status word (b200w4a4_last_device_status) and ends the kernel;
+ * nothing traps and the context stays usable. */
+int b200w4a4_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int timeout_ms, void* stream);
+
 /* Same result as b200w4a4_linear, for callers that cannot allocate device memory.
  * (No counterpart in the reference, whose ops allocate their intermediates with
  * torch::empty on every call.)

@@ -1,0 +1,101 @@
+"""qk_norm_rope_push + wait_flags: the K/V exchange of a row-sharded attention group done by the
+producing kernel (stores to every rank's gather buffer, then a completion flag) instead of a
+separate all-gather.  One GPU stands in for the whole group here: every "rank" owns a buffer, a
+flag array and a ticket in the same device memory and the ranks' kernels run one after the other on
+one stream, so no kernel ever waits for another one.  The time-out path is exercised with a flag
+that nothing sets."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from dsaquant_b200 import attention_qkv as aq
+    from dsaquant_b200.kernels import vdm_w4a4 as vdm
+
+    assert vdm.is_available(), vdm.load_error()
+    yield aq, vdm
+    assert vdm.last_device_status() == 0
+
+
+@pytest.mark.parametrize("ranks,D,heads", [(4, 1536, 12), (2, 5120, 40), (8, 256, 2)])
+def test_group_exchange_emulated_on_one_gpu(mods, ranks, D, heads):
+    aq, vdm = mods
+    from dsaquant_b200.sharding import row_partition
+
+    total = 2048 + 77
+    parts = row_partition(total, ranks)
+    hd = D // heads
+    g = torch.Generator(device="cuda").manual_seed(ranks + D)
+    x = torch.randn(total, D, generator=g, device="cuda").half()
+    w = (1 + 0.1 * torch.randn(D, generator=g, device="cuda")).half()
+    ang = torch.rand(total, 1, hd // 2, generator=g, device="cuda") * 6.28
+    cs = aq.rope_cos_sin(torch.polar(torch.ones_like(ang), ang))
+    bufs = [torch.full((total, D), -3.0, dtype=torch.bfloat16, device="cuda") for _ in range(ranks)]
+    flags = [torch.zeros(ranks, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    tickets = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    for epoch in (1, 2):
+        if epoch == 2:
+            x = (x.float() * 0.5 + 0.25).half()
+        want = aq.qk_norm_rope(x, w, cs, 1e-6, hd, torch.bfloat16)
+        for r, (s, e) in enumerate(parts):
+            if e == s:
+                continue
+            aq.qk_norm_rope_push(x[s:e], w, cs[s:e], 1e-6, hd, [b.data_ptr() for b in bufs], D, s, torch.bfloat16,
+                                 flag_ptrs=[f.data_ptr() for f in flags], flag_index=r, epoch=epoch, ticket=tickets[r])
+        live = [r for r, (s, e) in enumerate(parts) if e > s]
+        for r in range(ranks):
+            # every rank waits for the ranks that sent something (empty shards raise no flag)
+            aq.wait_flags(flags[r][:len(live)] if live == list(range(len(live))) else flags[r], epoch, 200)
+        torch.cuda.synchronize()
+        assert vdm.last_device_status() == 0
+        for r in range(ranks):
+            assert torch.equal(bufs[r], want)
+            assert (flags[r][live] == epoch).all()
+            assert int(tickets[r].item()) == 0
+
+
+def test_wait_that_runs_out_reports_a_status_and_leaves_the_context_usable(mods):
+    aq, vdm = mods
+    flags = torch.zeros(3, dtype=torch.int32, device="cuda")
+    flags[0] = 7
+    aq.wait_flags(flags, 7, timeout_ms=30)            # flags 1 and 2 never reach 7
+    torch.cuda.synchronize()
+    assert vdm.last_device_status() == 105
+    assert vdm.last_device_status() == 0              # read-and-clear
+    flags.fill_(9)                                    # later epochs pass (>= comparison)
+    aq.wait_flags(flags, 8, timeout_ms=30)
+    x = torch.randn(64, 256, device="cuda").half()
+    assert torch.equal(aq.qk_norm_rope(x, None, None, 1e-6, 128, torch.float16), x)
+    assert vdm.last_device_status() == 0
+
+
+def test_push_argument_checks(mods):
+    aq, _ = mods
+    from dsaquant_b200 import _lib
+
+    lib = _lib.load()
+    x = torch.zeros(8, 256, dtype=torch.float16, device="cuda")
+    o = torch.zeros(8, 256, dtype=torch.float16, device="cuda")
+    t = torch.zeros(1, dtype=torch.int32, device="cuda")
+    f = torch.zeros(4, dtype=torch.int32, device="cuda")
+    outs9 = (ctypes.c_void_p * 9)(*[o.data_ptr()] * 9)
+    flg = (ctypes.c_void_p * 9)(*[f.data_ptr()] * 9)
+    call = lib.b200w4a4_qk_norm_rope_push
+    assert call(x.data_ptr(), 256, None, None, 1e-6, 128, outs9, 9, 0, 256, 0, None, 0, 0, None, 8, 256, None) == -1
+    assert call(x.data_ptr(), 256, None, None, 1e-6, 128, outs9, 0, 0, 256, 0, None, 0, 0, None, 8, 256, None) == -1
+    assert call(x.data_ptr(), 256, None, None, 1e-6, 128, outs9, 2, 0, 256, 0, flg, 0, 1, None, 8, 256, None) == -1
+    assert call(x.data_ptr(), 256, None, None, 1e-6, 128, outs9, 2, 0, 256, -1, None, 0, 0, None, 8, 256, None) == -1
+    assert lib.b200w4a4_wait_flags(f.data_ptr(), 33, 1, 10, None) == -1
+    assert lib.b200w4a4_wait_flags(f.data_ptr(), 4, 1, 0, None) == -1
+    with pytest.raises(ValueError):
+        aq.qk_norm_rope_push(x, None, None, 1e-6, 128, [o.data_ptr()], 256, 0, torch.float16, flag_ptrs=[f.data_ptr()])
+    # plain two-destination push without flags
+    o2 = torch.ones(8, 256, dtype=torch.float16, device="cuda")
+    xr = torch.randn(8, 256, device="cuda").half()
+    aq.qk_norm_rope_push(xr, None, None, 1e-6, 128, [o.data_ptr(), o2.data_ptr()], 256, 0, torch.float16)
+    assert torch.equal(o, xr) and torch.equal(o2, xr)
