@@ -209,4 +209,25 @@ inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t str
   return cudaGetLastError();
 }
 
+// flag[d][index] = value on up to 8 flag arrays (this GPU's and peer-mapped ones), ordered after
+// everything the stream ran before this kernel: "I am done reading" / "my part is complete".
+struct SignalArgs {
+  uint32_t* flag[kMaxPushDestinations];
+  int n;
+  int index;
+  uint32_t value;
+};
+
+__global__ void signal_flags_kernel(const SignalArgs a) {
+  const int d = static_cast<int>(threadIdx.x);
+  if (d >= a.n) return;
+  uint32_t* p = nullptr;
+#pragma unroll
+  for (int i = 0; i < kMaxPushDestinations; ++i)
+    if (i == d) p = a.flag[i];
+  if (p == nullptr) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p + a.index), "r"(a.value) : "memory");
+}
+
 }  // namespace b200w4a4

@@ -595,6 +595,20 @@ int b200w4a4_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int timeou
   return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
 }
 
+int b200w4a4_signal_flags(uint32_t* const* flags, int n, int index, uint32_t value, void* stream) {
+  if (flags == nullptr || n < 1 || n > kMaxPushDestinations || index < 0) return B200W4A4_EINVAL;
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  SignalArgs a;
+  for (int d = 0; d < kMaxPushDestinations; ++d) a.flag[d] = d < n ? flags[d] : nullptr;
+  a.n = n;
+  a.index = index;
+  a.value = value;
+  signal_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
 int b200w4a4_linear_fused(const void* x_f16, int prologue, const float* mod_scale,
                           const float* mod_shift, long long mod_row_stride, float ln_eps,
                           const void* w_b200, const void* w_scale, const void* bias, void* out,

@@ -203,6 +203,11 @@ int b200w4a4_qk_norm_rope_push(const void* x_f16, long long x_ld, const void* no
  * nothing traps and the context stays usable. */
 int b200w4a4_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int timeout_ms, void* stream);
 
+/* Enqueues a kernel that writes `value` to flags[d][index] for d < n (n <= 8; NULL entries are
+ * skipped) with release semantics at system scope, ordered after all earlier work of the stream:
+ * the consumer's "done reading" signal that lets producers overwrite a gather buffer. */
+int b200w4a4_signal_flags(uint32_t* const* flags, int n, int index, uint32_t value, void* stream);
+
 /* Same result as b200w4a4_linear, for callers that cannot allocate device memory.
  * (No counterpart in the reference, whose ops allocate their intermediates with
  * torch::empty on every call.)

@@ -99,3 +99,64 @@ def test_push_argument_checks(mods):
     xr = torch.randn(8, 256, device="cuda").half()
     aq.qk_norm_rope_push(xr, None, None, 1e-6, 128, [o.data_ptr(), o2.data_ptr()], 256, 0, torch.float16)
     assert torch.equal(o, xr) and torch.equal(o2, xr)
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_exchange_protocol_over_several_blocks_emulated(mods, ranks):
+    """PeerKVExchange bookkeeping (epochs, the two buffer sets, ready / done flags) with every rank of
+    the group living in this process: four consecutive attention blocks, results equal to the
+    single-call kernel on the whole matrix, no wait runs out."""
+    aq, vdm = mods
+    from dsaquant_b200 import peer_exchange as px
+    from dsaquant_b200.sharding import row_partition, shard_capacity
+
+    D, heads, total = 512, 4, 1500
+    hd = D // heads
+    parts = row_partition(total, ranks)
+    cap = shard_capacity(total, ranks) * ranks
+    senders = sum(1 for s, e in parts if e > s)
+    mem = [torch.zeros(px.exchange_bytes(cap, D, ranks), dtype=torch.uint8, device="cuda") for _ in range(ranks)]
+    members = [px.layout(m.data_ptr(), cap, D, ranks) for m in mem]
+    group = [px.PeerKVExchange(r, members, mem[r], cap, D, parts[r][0], timeout_ms=200) for r in range(ranks)]
+    g = torch.Generator(device="cuda").manual_seed(ranks)
+    w = (1 + 0.1 * torch.randn(D, generator=g, device="cuda")).half()
+    ang = torch.rand(total, 1, hd // 2, generator=g, device="cuda") * 6.28
+    cs = aq.rope_cos_sin(torch.polar(torch.ones_like(ang), ang))
+    for block in range(4):
+        k = torch.randn(total, D, generator=g, device="cuda").half()
+        v = torch.randn(total, D, generator=g, device="cuda").half()
+        want_k = aq.qk_norm_rope(k, w, cs, 1e-6, hd)
+        want_v = v.to(torch.bfloat16)
+        for ex in group:
+            assert ex.begin_block() == block + 1
+        for r, ex in enumerate(group):
+            s, e = parts[r]
+            if e > s:
+                ex.push("v", v[s:e], None, None, 1e-6, hd)
+                ex.push("k", k[s:e], w, cs[s:e], 1e-6, hd)
+        for ex in group:
+            got_k, got_v = ex.gathered(total, senders)
+            assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
+        for ex in group:
+            ex.end_block()
+    torch.cuda.synchronize()
+    assert vdm.last_device_status() == 0
+
+
+def test_exchange_reports_a_missing_peer(mods):
+    aq, vdm = mods
+    from dsaquant_b200 import peer_exchange as px
+
+    D, ranks, cap = 256, 2, 512
+    mem = [torch.zeros(px.exchange_bytes(cap, D, ranks), dtype=torch.uint8, device="cuda") for _ in range(ranks)]
+    members = [px.layout(m.data_ptr(), cap, D, ranks) for m in mem]
+    ex0 = px.PeerKVExchange(0, members, mem[0], cap, D, 0, timeout_ms=30)
+    ex0.begin_block()
+    x = torch.randn(256, D, device="cuda").half()
+    ex0.push("v", x, None, None, 1e-6, 128)
+    ex0.push("k", x, None, None, 1e-6, 128)
+    ex0.gathered(512)                                  # rank 1 never pushes: both waits run out
+    torch.cuda.synchronize()
+    assert vdm.last_device_status() == 105
+    with pytest.raises(ValueError):
+        ex0.push("k", torch.zeros(600, D, device="cuda").half(), None, None, 1e-6, 128)
