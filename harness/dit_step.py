@@ -36,6 +36,9 @@ def main() -> None:
     ap.add_argument("--cond-only", action="store_true")
     ap.add_argument("--fused", action="store_true",
                     help="fold layer norm + modulation, GELU and gated skips into the W4A4 library calls")
+    ap.add_argument("--kv-push", action="store_true",
+                    help="with --fused and row sharding: K/V exchange by peer stores from the producing kernels "
+                         "(dsaquant_b200/peer_exchange.py) instead of NCCL all-gathers")
     args = ap.parse_args()
 
     import torch
@@ -74,6 +77,9 @@ def main() -> None:
             groups = [dist.new_group(list(range(0, half))), dist.new_group(list(range(half, world)))]
             branch = 0 if rank < half else 1
             branch_group = groups[branch] if half > 1 else None
+
+    if args.kv_push and args.fused and branch_group is not None:
+        model.enable_kv_push(branch_group)
 
     def step():
         if args.cond_only:
@@ -117,7 +123,9 @@ def main() -> None:
             "config": {"workload": f"{cfg.name} CFG step" + (" (cond only)" if args.cond_only else ""),
                        "tokens": m, "layers": L, "dim": d, "ffn": f, "heads": cfg.heads,
                        "parallelism": layout, "guidance": 5.0,
-                       "fused_elementwise": bool(args.fused)},
+                       "fused_elementwise": bool(args.fused),
+                       "kv_exchange": "peer stores" if (args.kv_push and args.fused and branch_group is not None)
+                       else ("nccl all-gather" if branch_group is not None else "none")},
             "w4a4_linear_tera_ops_per_step": forwards * per_fwd / 1e12,
             "output_finite": finite, "model_build_s": round(build_s, 1),
         }), flush=True)

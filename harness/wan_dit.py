@@ -218,19 +218,30 @@ def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
     eps = attn.norm_q.eps
     cs = None if freqs is None else torch.view_as_real(freqs).reshape(freqs.shape[0], -1)
     gather = group is not None and is_self
-    vb = qk_norm_rope(v[0], None, None, eps, hd)
-    if gather:
-        v_work, v_full = sharding.all_gather_rows(vb, m_total, group, async_op=True)
-    qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
-    kn = qk_norm_rope(k[0], attn.norm_k.weight, cs, eps, hd)
-    if gather:
-        kn = sharding.all_gather_rows(kn, m_total, group)
-        v_work.wait()
-        vb = v_full
+    exchange = getattr(attn, "kv_exchange", None) if gather else None
+    if exchange is not None:
+        # The kernels that produce K and V store their rows into every rank's gather buffer.
+        exchange.begin_block()
+        exchange.push("v", v[0], None, None, eps, hd)
+        exchange.push("k", k[0], attn.norm_k.weight, cs, eps, hd)
+        qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        kn, vb = exchange.gathered(m_total, attn.kv_senders)
+    else:
+        vb = qk_norm_rope(v[0], None, None, eps, hd)
+        if gather:
+            v_work, v_full = sharding.all_gather_rows(vb, m_total, group, async_op=True)
+        qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        kn = qk_norm_rope(k[0], attn.norm_k.weight, cs, eps, hd)
+        if gather:
+            kn = sharding.all_gather_rows(kn, m_total, group)
+            v_work.wait()
+            vb = v_full
     lq, lk = qn.shape[0], kn.shape[0]
     o = F.scaled_dot_product_attention(qn.view(1, lq, heads, hd).transpose(1, 2),
                                        kn.view(1, lk, heads, hd).transpose(1, 2),
                                        vb.view(1, lk, heads, hd).transpose(1, 2), dropout_p=0.0, is_causal=False)
+    if exchange is not None:
+        exchange.end_block()
     return o.transpose(1, 2).reshape(1, lq, d)
 
 
@@ -373,6 +384,20 @@ class WanDiT(nn.Module):
             blk.fused = bool(on)
 
     # ---- forward ------------------------------------------------------------------------
+    def enable_kv_push(self, group) -> None:
+        """Row-sharded self-attention exchanges K and V through peer memory (one PeerKVExchange shared
+        by all blocks) instead of two all-gathers per block.  Fused kernel route only."""
+        from dsaquant_b200.peer_exchange import PeerKVExchange
+
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        m_total = self.cfg.tokens
+        parts = sharding.row_partition(m_total, world)
+        cap = sharding.shard_capacity(m_total, world) * world
+        ex = PeerKVExchange.from_symmetric_memory(group, cap, self.cfg.dim, parts[rank][0])
+        for blk in self.blocks:
+            blk.attn1.kv_exchange = ex
+            blk.attn1.kv_senders = sum(1 for s, e in parts if e > s)
+
     def embed_time(self, timestep: torch.Tensor):
         half = self.cfg.freq_dim // 2
         freqs = torch.pow(10000, -torch.arange(half, dtype=torch.float64, device=timestep.device) / half)
