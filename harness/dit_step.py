@@ -106,6 +106,7 @@ def main() -> None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     assert vdm.last_device_status(local_rank) == 0
     finite = bool(torch.isfinite(out).all())
+    checksum = float(out.double().abs().sum().item())
 
     if rank == 0:
         d, f, L, m = cfg.dim, cfg.ffn, cfg.layers, cfg.tokens
@@ -127,7 +128,7 @@ def main() -> None:
                        "kv_exchange": "peer stores" if (args.kv_push and args.fused and branch_group is not None)
                        else ("nccl all-gather" if branch_group is not None else "none")},
             "w4a4_linear_tera_ops_per_step": forwards * per_fwd / 1e12,
-            "output_finite": finite, "model_build_s": round(build_s, 1),
+            "output_finite": finite, "output_abs_sum": checksum, "model_build_s": round(build_s, 1),
         }), flush=True)
     if world > 1:
         dist.barrier()
