@@ -318,3 +318,28 @@ print("ok")
                PYTHONPATH=str(ROOT))
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=str(tmp_path))
     assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
+
+
+def test_peer_exchange_layout_is_disjoint_and_sized():
+    """Host bookkeeping of the K/V exchange memory: regions are 256-byte aligned, do not overlap and
+    fit exactly in exchange_bytes; every rank's map has the same shape at its own base."""
+    from dsaquant_b200 import peer_exchange as px
+
+    for cap, dim, group in ((512, 256, 2), (32768, 5120, 4), (1280, 1536, 8)):
+        total = px.exchange_bytes(cap, dim, group)
+        base = 0x7000_0000_0000
+        m = px.layout(base, cap, dim, group)
+        regions = []
+        for p in range(2):
+            for i in range(2):
+                regions.append((m.kv[p][i], cap * dim * 2))
+                regions.append((m.ready[p][i], 4 * group))
+            regions.append((m.done[p], 4 * group))
+        assert len(regions) == 10
+        regions.sort()
+        for (a, n), (b, _) in zip(regions, regions[1:]):
+            assert a % 256 == 0 and a + n <= b
+        last, n = regions[-1]
+        assert base <= regions[0][0] and last + n <= base + total
+        other = px.layout(base + (1 << 32), cap, dim, group)
+        assert other.kv[1][1] - m.kv[1][1] == 1 << 32 and other.done[0] - m.done[0] == 1 << 32
