@@ -343,3 +343,32 @@ def test_peer_exchange_layout_is_disjoint_and_sized():
         assert base <= regions[0][0] and last + n <= base + total
         other = px.layout(base + (1 << 32), cap, dim, group)
         assert other.kv[1][1] - m.kv[1][1] == 1 << 32 and other.done[0] - m.done[0] == 1 << 32
+
+
+def test_public_header_is_plain_c(tmp_path):
+    """The drop-in boundary is a C ABI: the header must compile as C99 (and as C++) on its own,
+    and a C program must link against the library through it."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    from dsaquant_b200.csrc import build as b
+
+    src = tmp_path / "use_abi.c"
+    src.write_text('#include "b200w4a4.h"\n#include <stdio.h>\n'
+                   'int main(void) { printf("%d %s\\n", b200w4a4_version(), b200w4a4_strerror(-2));\n'
+                   '  return b200w4a4_repack_bytes(1536, 1536) == 1536u * 768u ? 0 : 1; }\n')
+    inc = str(ROOT / "include")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I", inc, str(src)],
+                   check=True)
+    gxx = shutil.which("g++")
+    if gxx is not None:
+        subprocess.run([gxx, "-std=c++11", "-fsyntax-only", "-x", "c++", "-I", inc, str(src)], check=True)
+    lib = b.lib_path()
+    exe = tmp_path / "use_abi"
+    subprocess.run([gcc, "-std=c99", "-I", inc, str(src), "-o", str(exe), str(lib), f"-Wl,-rpath,{lib.parent}"],
+                   check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.startswith("1 unsupported shape")
