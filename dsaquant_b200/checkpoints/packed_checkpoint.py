@@ -1,61 +1,100 @@
-"""vdm_w4a4_packed_v1 checkpoint helpers with the API of the reference module
-vdm_infer/checkpoints/packed_checkpoint.py (format tags :18-25, is_packed_checkpoint :28,
-load_quant_checkpoint :32-37, load_packed_quantized_model :52-148, enable_quant_kernels
-:151-164, enable_fused_qkv :167-188, packed_state_dict_from_model :190-199,
-save_packed_checkpoint :202-215).
+"""Reader / writer for `vdm_w4a4_packed_v1` checkpoints behind the function names of the reference
+module vdm_infer/checkpoints/packed_checkpoint.py (format tags :18-25, is_packed_checkpoint :28,
+load_quant_checkpoint :32-37, load_packed_quantized_model :52-148, enable_quant_kernels :151-164,
+enable_fused_qkv :167-188, packed_state_dict_from_model :190-199, save_packed_checkpoint :202-215).
 
-A packed checkpoint is `{"format": "vdm_w4a4_packed_v1", "metadata": {...}, "model": state_dict}`
-where every QuantLinear contributes `<name>.vdm_weight_packed` (u8 [N,K/2]),
-`<name>.vdm_weight_scale_packed` (f16 [N,K/64]), `<name>.vdm_weight_scale` (f16 [N]) and
-`<name>.bias`, and no fp `weight`.  The only addition here is the load-time repack: after the
-model has moved to its device each layer's v1 buffers are converted once into the layout the
-tcgen05 GEMM stages with TMA (`repack_for_b200=True`).
+File layout: `{"format": "vdm_w4a4_packed_v1", "metadata": {...}, "model": state_dict}`.  Each
+QuantLinear appears in the state dict as
+    <name>.vdm_weight_packed        u8  [N, K/2]    int4 codes in the v1 tile order
+    <name>.vdm_weight_scale_packed  f16 [N, K/64]   per-channel steps in the v1 lane order
+    <name>.vdm_weight_scale         f16 [N]         the same steps, plain
+    <name>.bias                     optional
+and has no floating-point `weight`.  An older export spells the buffers `diy_*`; both are read.
+
+What this module adds to the reference behaviour is one step at the end of loading: once the model
+sits on its CUDA device every layer's v1 buffers are repacked into the layout the tcgen05 GEMM
+stages with TMA (`repack_for_b200=True`), so the first forward does not pay for it.
 """
 from __future__ import annotations
 
 import gc
-from typing import Any
+from typing import Any, Dict, Iterable, List, Tuple
 
 import torch
 import torch.nn as nn
 
 PACKED_CHECKPOINT_FORMAT = "vdm_w4a4_packed_v1"
-_LEGACY_PACKED_CHECKPOINT_FORMAT = "vdm_" + "diy" + "_w4a4_packed_v1"
 VDM_BUFFER_SUFFIXES = ("vdm_weight_packed", "vdm_weight_scale_packed", "vdm_weight_scale")
-_LEGACY_BUFFER_SUFFIXES = tuple("diy_" + s[len("vdm_"):] for s in VDM_BUFFER_SUFFIXES)
-_QUANTIZER_MARKS = (".wquantizer.", ".aquantizer.")
+_LEGACY_PACKED_CHECKPOINT_FORMAT = PACKED_CHECKPOINT_FORMAT.replace("vdm_", "vdm_diy_", 1)
+_LEGACY_BUFFER_SUFFIXES = tuple(s.replace("vdm_", "diy_", 1) for s in VDM_BUFFER_SUFFIXES)
+_KNOWN_FORMATS = frozenset((PACKED_CHECKPOINT_FORMAT, _LEGACY_PACKED_CHECKPOINT_FORMAT))
+_BUFFER_ENDINGS = VDM_BUFFER_SUFFIXES + _LEGACY_BUFFER_SUFFIXES
 
 
 def is_packed_checkpoint(ckpt: Any) -> bool:
-    if not isinstance(ckpt, dict) or "model" not in ckpt:
-        return False
-    return ckpt.get("format") in (PACKED_CHECKPOINT_FORMAT, _LEGACY_PACKED_CHECKPOINT_FORMAT)
+    return isinstance(ckpt, dict) and "model" in ckpt and ckpt.get("format") in _KNOWN_FORMATS
 
 
 def load_quant_checkpoint(path: str, dcp_loader) -> dict:
-    """A `.pt`/`.pth` file is read with torch.load (CPU, weights only); anything else goes
-    through `dcp_loader` (distributed-checkpoint directory)."""
-    if path.endswith((".pt", ".pth")):
-        print(f"Loading torch checkpoint from {path}")
-        return torch.load(path, map_location="cpu", weights_only=True)
-    return dcp_loader(path)
+    """`.pt` / `.pth`: torch.load on the CPU, tensors only.  Any other path is a distributed
+    checkpoint directory and goes to `dcp_loader`."""
+    if not path.endswith((".pt", ".pth")):
+        return dcp_loader(path)
+    print(f"Loading torch checkpoint from {path}")
+    return torch.load(path, map_location="cpu", weights_only=True)
 
 
-def _key(module_name: str, suffix: str) -> str:
-    return f"{module_name}.{suffix}" if module_name else suffix
+# ----------------------------------------------------------------------------- key handling
+def _belongs_to_quantizer(key: str) -> bool:
+    return ".wquantizer." in key or ".aquantizer." in key
 
 
-def _set_buffer(module: nn.Module, name: str, tensor: torch.Tensor) -> None:
+def _join(prefix: str, leaf: str) -> str:
+    return leaf if not prefix else prefix + "." + leaf
+
+
+def _layer_buffers(state: Dict[str, torch.Tensor], layer_name: str) -> Tuple[Dict[str, torch.Tensor], List[str]]:
+    """The three buffers of one layer (current spelling preferred, legacy accepted) and the keys
+    that the checkpoint lacks."""
+    found: Dict[str, torch.Tensor] = {}
+    lacking: List[str] = []
+    for current, legacy in zip(VDM_BUFFER_SUFFIXES, _LEGACY_BUFFER_SUFFIXES):
+        for key in (_join(layer_name, current), _join(layer_name, legacy)):
+            if key in state:
+                found[current] = state[key]
+                break
+        else:
+            lacking.append(_join(layer_name, legacy))
+    return found, lacking
+
+
+def _replace_buffer(module: nn.Module, name: str, tensor: torch.Tensor) -> None:
     module._buffers.pop(name, None)
     if hasattr(module, name):
         delattr(module, name)
     module.register_buffer(name, tensor.detach().contiguous())
 
 
-def _is_quant_state(key: str) -> bool:
-    return any(mark in key for mark in _QUANTIZER_MARKS)
+def _switch_layer_to_packed(layer: nn.Module, buffers: Dict[str, torch.Tensor]) -> None:
+    """Attach the packed buffers and drop what they replace (fp weight, both fake quantisers)."""
+    for name, tensor in buffers.items():
+        _replace_buffer(layer, name, tensor)
+    layer.use_vdm_kernel = True
+    layer.use_kernel = layer.use_kernel_fused = False
+    layer.set_quant_state(use_wq=True, use_aq=True)
+    if getattr(layer, "weight", None) is not None:
+        layer.register_parameter("weight", None)
+    for attr in ("wquantizer", "aquantizer"):
+        if hasattr(layer, attr):
+            delattr(layer, attr)
+            setattr(layer, attr, None)
 
 
+def _quant_layers(model: nn.Module, cls: type) -> Iterable[Tuple[str, nn.Module]]:
+    return ((n, m) for n, m in model.named_modules() if isinstance(m, cls))
+
+
+# ----------------------------------------------------------------------------- loader
 def load_packed_quantized_model(
     model: nn.Module,
     packed_ckpt: dict,
@@ -66,78 +105,64 @@ def load_packed_quantized_model(
     require_vdm_kernel: bool = True,
     repack_for_b200: bool = True,
 ) -> tuple[list[str], list[str]]:
-    """Populate a freshly built model (its Linear layers already swapped for QuantLinear) from
-    a packed checkpoint; returns (missing, unexpected) keys of the non-quantised part."""
+    """Fills a freshly built model, whose Linear layers are already QuantLinear, from a packed
+    checkpoint.  Returns the (missing, unexpected) keys of the part that is not quantised."""
     if not is_packed_checkpoint(packed_ckpt):
-        found = packed_ckpt.get("format") if isinstance(packed_ckpt, dict) else type(packed_ckpt)
-        raise ValueError(f"Unsupported checkpoint format: {found}")
+        got = packed_ckpt.get("format") if isinstance(packed_ckpt, dict) else type(packed_ckpt)
+        raise ValueError(f"Unsupported checkpoint format: {got}")
     if require_vdm_kernel:
-        from dsaquant_b200.kernels.vdm_w4a4 import is_available, load_error
+        from dsaquant_b200.kernels import vdm_w4a4
 
-        assert is_available(), f"DSAQuant W4A4 kernel not compiled/available: {load_error()}"
+        assert vdm_w4a4.is_available(), f"DSAQuant W4A4 kernel not compiled/available: {vdm_w4a4.load_error()}"
 
     state = packed_ckpt["model"]
-    qlayers = {name: mod for name, mod in model.named_modules() if isinstance(mod, quant_linear_cls)}
-    fp_weight_keys = {_key(name, "weight") for name in qlayers}
-    all_suffixes = VDM_BUFFER_SUFFIXES + _LEGACY_BUFFER_SUFFIXES
+    layers = dict(_quant_layers(model, quant_linear_cls))
+    fp_weights = {_join(name, "weight") for name in layers}
 
-    plain = {k: v for k, v in state.items()
-             if not k.endswith(all_suffixes) and not _is_quant_state(k)
-             and not k.endswith("._bias_half") and k not in fp_weight_keys}
-    missing, unexpected = model.load_state_dict(plain, strict=False, assign=True)
-    missing = [k for k in missing if k not in fp_weight_keys and not _is_quant_state(k)]
+    # 1. everything that is not part of a quantised layer goes through load_state_dict
+    ordinary = {key: value for key, value in state.items()
+                if key not in fp_weights and not key.endswith(_BUFFER_ENDINGS)
+                and not key.endswith("._bias_half") and not _belongs_to_quantizer(key)}
+    missing, unexpected = model.load_state_dict(ordinary, strict=False, assign=True)
+    missing = [key for key in missing if key not in fp_weights and not _belongs_to_quantizer(key)]
 
-    absent: list[str] = []
-    loaded = 0
-    for name, mod in qlayers.items():
-        chosen = {}
-        for suffix, legacy in zip(VDM_BUFFER_SUFFIXES, _LEGACY_BUFFER_SUFFIXES):
-            k_new, k_old = _key(name, suffix), _key(name, legacy)
-            chosen[suffix] = k_new if k_new in state else k_old
-        lacking = [k for k in chosen.values() if k not in state]
+    # 2. the quantised layers take their three buffers
+    absent: List[str] = []
+    attached = 0
+    for name, layer in layers.items():
+        buffers, lacking = _layer_buffers(state, name)
         if lacking:
-            absent.extend(lacking)
+            absent += lacking
             continue
-        for suffix, k in chosen.items():
-            _set_buffer(mod, suffix, state[k])
-        mod.use_vdm_kernel, mod.use_kernel, mod.use_kernel_fused = True, False, False
-        mod.set_quant_state(use_wq=True, use_aq=True)
-        if getattr(mod, "weight", None) is not None:
-            mod.register_parameter("weight", None)
-        for qname in ("wquantizer", "aquantizer"):
-            if hasattr(mod, qname):
-                delattr(mod, qname)
-                setattr(mod, qname, None)
-        loaded += 1
-
+        _switch_layer_to_packed(layer, buffers)
+        attached += 1
     if absent:
         raise KeyError(f"Packed checkpoint is missing {len(absent)} VDM buffers, e.g. {', '.join(absent[:8])}")
-    if loaded == 0:
+    if attached == 0:
         raise RuntimeError("No QuantLinear layers were populated from the packed checkpoint")
-
-    del state, plain
+    del state, ordinary
     gc.collect()
 
+    # 3. move, then per-layer device-side preparation
     model = model.to(dtype).to(device)
-    for mod in model.modules():
-        if isinstance(mod, quant_linear_cls):
-            if mod.bias is not None:
-                mod._bias_half = mod.bias.half().contiguous()
-            if repack_for_b200 and torch.device(device).type == "cuda":
-                mod.prepare_b200_weights()
-    print(f"Loaded packed DSAQuant W4A4 checkpoint: {loaded} QuantLinear layers")
+    on_gpu = torch.device(device).type == "cuda"
+    for _, layer in _quant_layers(model, quant_linear_cls):
+        if layer.bias is not None:
+            layer._bias_half = layer.bias.half().contiguous()
+        if repack_for_b200 and on_gpu:
+            layer.prepare_b200_weights()
+    print(f"Loaded packed DSAQuant W4A4 checkpoint: {attached} QuantLinear layers")
     return list(missing), list(unexpected)
 
 
+# ----------------------------------------------------------------------------- switches on a live model
 def enable_quant_kernels(model: nn.Module, *, quant_linear_cls: type[nn.Module]) -> None:
     print("Enabling DSAQuant W4A4 kernel mode...")
-    for name, mod in model.named_modules():
-        if not isinstance(mod, quant_linear_cls):
-            continue
-        mod.set_quant_state(use_wq=True, use_aq=True)
+    for name, layer in _quant_layers(model, quant_linear_cls):
+        layer.set_quant_state(use_wq=True, use_aq=True)
         try:
-            mod.enable_vdm_kernel_mode()
-        except Exception as exc:
+            layer.enable_vdm_kernel_mode()
+        except Exception as exc:  # keep going: the reference reports and continues (:161-164)
             print(f"  Failed to enable VDM kernel for {name}: {exc}")
 
 
@@ -146,27 +171,31 @@ def enable_fused_qkv(model: nn.Module, *, quant_linear_cls: type[nn.Module],
     if not use_fused_qkv:
         return
     print("Enabling fused QKV kernel (vdm)...")
-    for mod in model.modules():
-        if not isinstance(mod, attention_cls):
-            continue
-        projs = (mod.to_q, mod.to_k, mod.to_v)
-        if all(isinstance(p, quant_linear_cls) and p.use_vdm_kernel for p in projs):
-            mod.use_fused_qkv_kernel = True
-            mod.qkv_kernel_backend = "vdm"
+
+    def ready(proj) -> bool:
+        return isinstance(proj, quant_linear_cls) and bool(proj.use_vdm_kernel)
+
+    for attn in model.modules():
+        if isinstance(attn, attention_cls) and ready(attn.to_q) and ready(attn.to_k) and ready(attn.to_v):
+            attn.use_fused_qkv_kernel = True
+            attn.qkv_kernel_backend = "vdm"
 
 
+# ----------------------------------------------------------------------------- writer
 def packed_state_dict_from_model(model: nn.Module, *, float_dtype: torch.dtype = torch.float16) -> dict[str, torch.Tensor]:
-    packed: dict[str, torch.Tensor] = {}
+    """State dict as the packed format stores it: CPU tensors, floating point cast to
+    `float_dtype`, without fake-quantiser state and without the derived fp16 bias copies."""
+    out: dict[str, torch.Tensor] = {}
     for key, value in model.state_dict().items():
-        if _is_quant_state(key) or key.endswith("._bias_half"):
+        if key.endswith("._bias_half") or _belongs_to_quantizer(key):
             continue
-        t = value.detach().cpu().contiguous()
-        packed[key] = t.to(float_dtype) if t.is_floating_point() else t
-    return packed
+        host = value.detach().cpu().contiguous()
+        out[key] = host.to(float_dtype) if host.is_floating_point() else host
+    return out
 
 
 def save_packed_checkpoint(model: nn.Module, output_path: str, *, metadata: dict[str, Any] | None = None,
                            float_dtype: torch.dtype = torch.float16) -> None:
-    torch.save({"format": PACKED_CHECKPOINT_FORMAT, "metadata": metadata or {},
-                "model": packed_state_dict_from_model(model, float_dtype=float_dtype)}, output_path)
+    state = packed_state_dict_from_model(model, float_dtype=float_dtype)
+    torch.save({"format": PACKED_CHECKPOINT_FORMAT, "metadata": dict(metadata or {}), "model": state}, output_path)
     print(f"Saved packed checkpoint to {output_path}")
