@@ -41,6 +41,8 @@ SIGNATURES = {
     "b200w4a4_unpack_codes": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200w4a4_set_cta_group": (c_int, [c_int]),
     "b200w4a4_last_device_status": (c_int, [c_int]),
+    "b200w4a4_check_device": (c_int, [c_int]),
+    "b200w4a4_map_cache_stats": (None, [POINTER(ctypes.c_ulonglong), POINTER(ctypes.c_ulonglong)]),
 }
 
 _LIB: Optional[ctypes.CDLL] = None
@@ -56,7 +58,10 @@ class B200W4A4Error(RuntimeError):
 
 
 def load() -> ctypes.CDLL:
-    """Loads (building first if the in-tree library is missing and nvcc exists). Raises on failure."""
+    """Loads the in-tree library, rebuilding it first when it is missing or older than its
+    sources.  A stale library is never loaded silently: without nvcc it is refused.
+    B200W4A4_NO_JIT=1 means "use the prebuilt file as it is": nothing is built or compared.
+    Raises on failure."""
     global _LIB, _LOAD_ERROR
     if _LIB is not None:
         return _LIB
@@ -65,9 +70,13 @@ def load() -> ctypes.CDLL:
             return _LIB
         try:
             path = _build.lib_path()
-            if not path.exists():
-                if os.environ.get("B200W4A4_NO_JIT", "0") == "1":
+            no_jit = os.environ.get("B200W4A4_NO_JIT", "0") == "1"
+            if no_jit:
+                if not path.exists():
                     raise FileNotFoundError(f"{path} is missing and B200W4A4_NO_JIT=1")
+            elif _build.is_stale(path):
+                if _build.nvcc_path() is None:
+                    raise RuntimeError(f"{path} is missing or older than its sources and nvcc was not found")
                 path = _build.build()
             lib = ctypes.CDLL(str(path))
             for name, (res, args) in SIGNATURES.items():

@@ -141,12 +141,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRope
     }
   }
   if (PUSH && a.ticket != nullptr) {
-    // Publish: every CTA fences its stores system-wide, then takes a ticket; the CTA that takes
-    // the last one knows (through the atomic chain) that all stores of the launch are ordered
-    // before its own flag writes.
-    __threadfence_system();
+    // Publish: the barrier orders every thread's stores before thread 0, whose system-wide
+    // fence then covers them all (fences are cumulative), and the ticket chain orders every
+    // CTA's fence before the flag writes of the CTA that draws the last ticket.
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const unsigned int t_last = gridDim.x - 1;
       if (atomicAdd(a.ticket, 1u) == t_last) {
         *a.ticket = 0u;

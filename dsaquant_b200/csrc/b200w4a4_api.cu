@@ -7,8 +7,11 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <string.h>
+
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 
 #include "../../include/b200w4a4.h"
 #include "attn_glue.cuh"
@@ -22,8 +25,12 @@ using namespace b200w4a4;
 
 constexpr int kMaxDevices = 64;
 
-// Device status word: kernels write a role code here when a bounded wait runs out.
+// Device status word: kernels write a role code here when a bounded wait runs out.  It is a
+// report for the host (b200w4a4_last_device_status / b200w4a4_check_device) and cancels nothing.
 __device__ int g_device_status;
+// Id of the GEMM launch that last timed out: the other CTAs of that launch, and only they,
+// drain early when they see their own id here.
+__device__ unsigned g_gemm_abort;
 
 std::atomic<int> g_cta_group{0};  // 0 = not chosen yet (environment decides on first use)
 
@@ -32,6 +39,8 @@ struct DeviceState {
   int err = B200W4A4_OK;
   int sm_count = 0;
   int* status_ptr = nullptr;
+  unsigned* abort_ptr = nullptr;
+  std::atomic<unsigned> launch_seq{0};
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -85,7 +94,13 @@ int device_state(DeviceState** out) {
       return;
     }
     st.status_ptr = static_cast<int*>(p);
-    if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess ||
+    void* ab = nullptr;
+    if (cudaGetSymbolAddress(&ab, g_gemm_abort) != cudaSuccess) {
+      st.err = B200W4A4_ECUDA;
+      return;
+    }
+    st.abort_ptr = static_cast<unsigned*>(ab);
+    if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess || cudaMemset(ab, 0, sizeof(unsigned)) != cudaSuccess ||
         !set_gemm_smem<1, EPI_NONE>() || !set_gemm_smem<2, EPI_NONE>() ||
         !set_gemm_smem<1, EPI_GELU_TANH>() || !set_gemm_smem<2, EPI_GELU_TANH>() ||
         !set_gemm_smem<1, EPI_GATE_RESIDUAL>() || !set_gemm_smem<2, EPI_GATE_RESIDUAL>() ||
@@ -116,9 +131,9 @@ int check_nk(int N, int K) {
   return B200W4A4_OK;
 }
 
-int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner,
-              uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
-              CUtensorMapSwizzle sw) {
+int encode_2d_uncached(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner,
+                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                       uint32_t box_outer, CUtensorMapSwizzle sw) {
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return B200W4A4_ECUDA;
   const cuuint64_t dims[2] = {inner, outer};
@@ -129,6 +144,57 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64
                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+// Tensor maps are a pure function of (address, extents, pitch, box, element type, swizzle), and a
+// model calls the same layers with the same buffers step after step, so encoded maps are kept
+// in a small mutex-guarded table instead of being re-encoded by the driver on every launch.
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, pitch;
+  uint32_t box_inner, box_outer;
+  int dt, sw;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch &&
+           box_inner == o.box_inner && box_outer == o.box_outer && dt == o.dt && sw == o.sw;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.inner + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.outer * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2));
+    h ^= (k.pitch + (static_cast<uint64_t>(k.box_outer) << 32) + k.box_inner + (h << 6) + (h >> 2));
+    h ^= static_cast<uint64_t>(k.dt * 31 + k.sw);
+    return static_cast<size_t>(h);
+  }
+};
+constexpr size_t kMapCacheLimit = 8192;  // entries (128 B each); the table is emptied when full
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+std::atomic<unsigned long long> g_map_hits{0}, g_map_misses{0};
+
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner,
+              uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+              CUtensorMapSwizzle sw) {
+  const MapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, static_cast<int>(dt),
+                   static_cast<int>(sw)};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      memcpy(map, &it->second, sizeof(CUtensorMap));
+      g_map_hits.fetch_add(1, std::memory_order_relaxed);
+      return B200W4A4_OK;
+    }
+  }
+  const int rc = encode_2d_uncached(map, dt, base, inner, outer, row_stride_bytes, box_inner, box_outer, sw);
+  if (rc != B200W4A4_OK) return rc;
+  g_map_misses.fetch_add(1, std::memory_order_relaxed);
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() >= kMapCacheLimit) g_map_cache.clear();
+  g_map_cache.emplace(key, *map);
+  return B200W4A4_OK;
 }
 
 struct EpiArgs {
@@ -142,7 +208,7 @@ struct EpiArgs {
 };
 
 template <int CG, int EPI = EPI_NONE>
-int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
+int launch_gemm(DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
                 const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
                 int N, int K, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
   using C = GemmCfg<CG>;
@@ -152,9 +218,15 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
                      static_cast<uint64_t>(M), static_cast<uint64_t>(K), C::BK, C::BM,
                      CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200W4A4_OK) return rc;
+#if B200W4A4_ABL_W8
+  rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K),
+                 static_cast<uint64_t>(N), static_cast<uint64_t>(K), C::BK, C::B_ROWS,
+                 CU_TENSOR_MAP_SWIZZLE_128B);
+#else
   rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K / 2),
                  static_cast<uint64_t>(N), static_cast<uint64_t>(K / 2), C::BK / 2, C::B_ROWS,
                  CU_TENSOR_MAP_SWIZZLE_NONE);
+#endif
   if (rc != B200W4A4_OK) return rc;
   if constexpr (EPI == EPI_SPLIT) {
     const int seg_cols = N / epi.segments;
@@ -185,6 +257,10 @@ int launch_gemm(const DeviceState& st, const void* qact, const float* act_scale,
   p.m_tiles = (M + C::BM * CG - 1) / (C::BM * CG);
   p.n_tiles = (N + C::BN - 1) / C::BN;
   p.status = st.status_ptr;
+  p.abort_word = st.abort_ptr;
+  unsigned id = st.launch_seq.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (id == 0) id = st.launch_seq.fetch_add(1, std::memory_order_relaxed) + 1;  // 0 means "no launch"
+  p.launch_id = id;
   p.residual = epi.residual;
   p.gate = epi.gate;
   p.gate_row_stride = epi.gate_row_stride;
@@ -642,8 +718,11 @@ int b200w4a4_linear_noalloc(const void* x, int x_dtype, const void* w_b200, cons
   if (M < 1 || K < 64 || (K % 64) != 0) return B200W4A4_ESHAPE;
   if (M > kNoAllocMaxRows || static_cast<size_t>(M) * static_cast<size_t>(K) > kNoAllocCodeBytes)
     return B200W4A4_ELIMIT;
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);  // a device that is not 10.0 answers EARCH before any symbol look-up
+  if (rc != B200W4A4_OK) return rc;
   uint8_t* base = nullptr;
-  int rc = noalloc_scratch(&base);
+  rc = noalloc_scratch(&base);
   if (rc != B200W4A4_OK) return rc;
   void* qact = base;
   float* act_scale = reinterpret_cast<float*>(base + kNoAllocCodeBytes);
@@ -689,6 +768,32 @@ int b200w4a4_set_cta_group(int cta_group) {
   const int prev = current_cta_group();
   g_cta_group.store(cta_group, std::memory_order_relaxed);
   return prev;
+}
+
+void b200w4a4_map_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+  if (hits != nullptr) *hits = g_map_hits.load(std::memory_order_relaxed);
+  if (misses != nullptr) *misses = g_map_misses.load(std::memory_order_relaxed);
+}
+
+int b200w4a4_check_device(int device) {
+  int prev = 0;
+  if (cudaGetDevice(&prev) != cudaSuccess) return B200W4A4_ECUDA;
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return B200W4A4_ECUDA;
+  }
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc == B200W4A4_OK) {
+    int value = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(&value, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+      rc = B200W4A4_ECUDA;
+    else if (value != 0)
+      rc = B200W4A4_EDEVICE;  // the code itself stays readable through b200w4a4_last_device_status
+  }
+  cudaSetDevice(prev);
+  return rc;
 }
 
 int b200w4a4_last_device_status(int device) {

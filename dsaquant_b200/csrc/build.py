@@ -49,6 +49,11 @@ def is_stale(lib: Path) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the library unless it is newer than its sources.  Several processes may call this
+    at once (one rank per GPU): a file lock lets one of them compile while the others wait, and
+    the result is moved into place atomically so nobody maps a half-written file."""
+    import fcntl
+
     lib = lib_path()
     if not force and not is_stale(lib):
         return lib
@@ -56,15 +61,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libb200w4a4.so (set CUDA_HOME)")
     lib.parent.mkdir(parents=True, exist_ok=True)
-    cmd = [nvcc, *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(lib), *[str(CSRC / s) for s in SOURCES]]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
-    if verbose:
-        print(proc.stderr)
+    with open(lib.with_suffix(".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale(lib):   # another process built it while this one waited
+                return lib
+            tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
+            cmd = [nvcc, *NVCC_FLAGS]
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+            cmd += ["-o", str(tmp), *[str(CSRC / s) for s in SOURCES]]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
+            os.replace(tmp, lib)
+            if verbose:
+                print(proc.stderr)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return lib
 
 

@@ -31,6 +31,17 @@
 
 #include "ptx.cuh"
 
+// Build-time switches used while measuring variants (scratch builds only).
+#ifndef B200W4A4_OPT_L2HINT
+#define B200W4A4_OPT_L2HINT 1
+#endif
+#ifndef B200W4A4_OPT_FENCE_KB0
+#define B200W4A4_OPT_FENCE_KB0 0
+#endif
+#ifndef B200W4A4_ABL_W8
+#define B200W4A4_ABL_W8 0
+#endif
+
 namespace b200w4a4 {
 
 // Device status codes written by a kernel whose bounded wait ran out.
@@ -106,7 +117,9 @@ struct GemmParams {
   int32_t* acc_dump;        // [M,N] int32 or null (tests)
   int M, N, K;
   int m_tiles, n_tiles;     // in units of (CG*128) rows and 256 columns
-  int* status;              // device status word
+  int* status;              // device status word: first time-out code of any launch (report only)
+  unsigned* abort_word;     // holds the id of the launch that last timed out
+  unsigned launch_id;       // id of this launch (never 0): only its own time-out cancels it
   // epilogue extras (see the EPI_* variants)
   const __half* residual;   // [M,N] fp16, may alias the output
   const float* gate;        // [N] (or [M,N] with gate_row_stride = N)
@@ -133,28 +146,38 @@ namespace detail {
 
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 
-// Bounded wait on an mbarrier phase.  On time-out records `code` once, raises
-// the CTA-local abort flag and returns false; every other role sees the flag
-// (or the global status word) in its own wait and drains too.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                         int* status, int code) {
+// What a bounded wait needs to give up cleanly.  The status word is only a report (it keeps the
+// first code until the host reads it, and other kernels write to it too), so it never cancels a
+// launch; the abort word does, and only for the launch whose id it holds.
+struct WaitCtx {
+  volatile int* abort_flag;  // CTA-local, shared memory
+  int* status;
+  unsigned* abort_word;
+  unsigned launch_id;
+};
+
+// Bounded wait on an mbarrier phase.  On time-out records `code` once, publishes this launch's
+// id in the abort word, raises the CTA-local abort flag and returns false; every other role sees
+// the flag (or, in another CTA, the abort word) in its own wait and drains too.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
   if (ptx::mbar_probe(bar, parity)) return true;
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (true) {
     if (ptx::mbar_test(bar, parity)) return true;
     if ((++spins & 0x3FF) == 0) {
-      if (*abort_flag) return false;
-      if (*reinterpret_cast<volatile int*>(status) != 0) {
-        *abort_flag = 1;
+      if (*w.abort_flag) return false;
+      if (*reinterpret_cast<volatile unsigned*>(w.abort_word) == w.launch_id) {
+        *w.abort_flag = 1;
         return false;
       }
       uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
       } else if (now - t0 > kWaitLimitNs) {
-        atomicCAS(status, 0, code);
-        *abort_flag = 1;
+        atomicCAS(w.status, 0, code);
+        atomicExch(w.abort_word, w.launch_id);
+        *w.abort_flag = 1;
         return false;
       }
     }
@@ -250,10 +273,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_gen + C::OFF_BAR + 8 * (C::NUM_BARS - 1));
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
+  const detail::WaitCtx wctx{abort_flag, p.status, p.abort_word, p.launch_id};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::S; ++s) {
-      ptx::mbar_init(bar_full(s), C::UNPACK_WARPS * CG + 1);  // unpack warps + the A producer
+      ptx::mbar_init(bar_full(s), B200W4A4_ABL_W8 ? 1 : C::UNPACK_WARPS * CG + 1);  // unpack warps + the A producer
       ptx::mbar_init(bar_consumed(s), 1);                     // one MMA commit
     }
     for (int s = 0; s < C::SB; ++s) {
@@ -302,12 +326,27 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
         const int m0 = mt * (C::BM * CG) + static_cast<int>(cta_rank) * C::BM;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, abort_flag, p.status,
+          if (!detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, wctx,
                                 DEV_TIMEOUT_PRODUCER)) {
             alive = false;
             break;
           }
           const uint32_t dst = smem_base + C::OFF_MAIN + pos.slot * C::STAGE_BYTES;
+#if B200W4A4_ABL_W8
+          const int n0w = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
+          if constexpr (CG == 1) {
+            ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES + C::BU_BYTES);
+            ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
+            ptx::tma_load_2d(dst + C::A_BYTES, &tm_w, bar_full(pos.slot), kb * C::BK, n0w);
+          } else {
+            if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * (C::A_BYTES + C::BU_BYTES));
+            uint32_t remote = full_remote[0];
+#pragma unroll
+            for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
+            ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
+            ptx::tma_load_2d_pair(dst + C::A_BYTES, &tm_w, remote, kb * C::BK, n0w);
+          }
+#else
           if constexpr (CG == 1) {
             ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES);
             ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
@@ -318,6 +357,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
             ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
           }
+#endif
           pos.advance();
         }
       }
@@ -330,22 +370,31 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp == C::WARP_B_PRODUCER) {
     // ===================== TMA producer: packed int4 weights =====================
-    if (lane == 0) {
+    if (lane == 0 && !B200W4A4_ABL_W8) {
       RingPos<C::SB> pos;
       bool alive = true;
+#if B200W4A4_OPT_L2HINT
+      // Weights are re-read by every row tile: ask L2 to keep them while outputs stream through.
+      const uint64_t keep = ptx::l2_policy_evict_last();
+#endif
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
         int mt, nt;
         tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
         const int n0 = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!detail::wait_bar(bar_bp_free(pos.slot), pos.phase ^ 1, abort_flag, p.status,
+          if (!detail::wait_bar(bar_bp_free(pos.slot), pos.phase ^ 1, wctx,
                                 DEV_TIMEOUT_PRODUCER)) {
             alive = false;
             break;
           }
           ptx::mbar_arrive_expect_tx(bar_bp_full(pos.slot), C::BP_BYTES);
+#if B200W4A4_OPT_L2HINT
+          ptx::tma_load_2d_hint(smem_base + C::OFF_BP + pos.slot * C::BP_BYTES, &tm_w,
+                                bar_bp_full(pos.slot), kb * (C::BK / 2), n0, keep);
+#else
           ptx::tma_load_2d(smem_base + C::OFF_BP + pos.slot * C::BP_BYTES, &tm_w,
                            bar_bp_full(pos.slot), kb * (C::BK / 2), n0);
+#endif
           pos.advance();
         }
       }
@@ -384,18 +433,22 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           if (!running) break;
           if (kb == 0) {
             const uint32_t ab = local_tile & 1;
-            if (!detail::wait_bar(bar_acc_free(ab), ((local_tile >> 1) & 1) ^ 1, abort_flag, p.status,
-                                  DEV_TIMEOUT_MMA)) {
+            if (!detail::wait_bar(bar_acc_free(ab), ((local_tile >> 1) & 1) ^ 1, wctx, DEV_TIMEOUT_MMA)) {
               running = false;
               break;
             }
             tmem_d = tmem_base + ab * C::BN;
+#if B200W4A4_OPT_FENCE_KB0
+            ptx::tc_fence_after_sync();  // orders the epilogue's TMEM reads before this tile's MMAs
+#endif
           }
-          if (!detail::wait_bar(bar_full(s), phase, abort_flag, p.status, DEV_TIMEOUT_MMA)) {
+          if (!detail::wait_bar(bar_full(s), phase, wctx, DEV_TIMEOUT_MMA)) {
             running = false;
             break;
           }
+#if !B200W4A4_OPT_FENCE_KB0
           ptx::tc_fence_after_sync();
+#endif
           // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
           const uint32_t a_lo = a_lo0 + s * (C::STAGE_BYTES >> 4), b_lo = b_lo0 + s * (C::STAGE_BYTES >> 4);
           ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kb > 0 ? 1u : 0u);
@@ -423,13 +476,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t lo_off = (((c2 + 1) ^ row_x) << 4);
     RingPos<C::S> pos;
     RingPos<C::SB> bpos;
-    bool alive = true;
+    bool alive = !B200W4A4_ABL_W8;
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
       for (int kb = 0; kb < kblocks; ++kb) {
-        if (!detail::wait_bar(bar_bp_full(bpos.slot), bpos.phase, abort_flag, p.status,
-                              DEV_TIMEOUT_UNPACK) ||
-            !detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, abort_flag, p.status,
-                              DEV_TIMEOUT_UNPACK)) {
+        if (!detail::wait_bar(bar_bp_full(bpos.slot), bpos.phase, wctx, DEV_TIMEOUT_UNPACK) ||
+            !detail::wait_bar(bar_consumed(pos.slot), pos.phase ^ 1, wctx, DEV_TIMEOUT_UNPACK)) {
           alive = false;
           break;
         }
@@ -474,6 +525,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t row_sw = static_cast<uint32_t>(lane & 7);
     uint32_t local_tile = 0;
     bool alive = true;
+#if B200W4A4_OPT_L2HINT
+    // The output is written once and not read by this kernel: evict it first, so that it does
+    // not push the weights (re-read by every row tile) out of L2.
+    const uint64_t stream_out = ptx::l2_policy_evict_first();
+#endif
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
       int mt, nt;
       tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
@@ -481,7 +537,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int n0 = nt * C::BN;
       const uint32_t ab = local_tile & 1;
       const uint32_t aph = (local_tile >> 1) & 1;
-      if (!detail::wait_bar(bar_acc_full(ab), aph, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
+      if (!detail::wait_bar(bar_acc_full(ab), aph, wctx, DEV_TIMEOUT_EPILOGUE)) {
         alive = false;
         break;
       }
@@ -597,9 +653,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               if constexpr (EPI == EPI_SPLIT) {
                 // seg_cols is a multiple of the 64-column store box, so a box lies in one segment.
                 const int sgm = c_store / p.seg_cols;
+#if B200W4A4_OPT_L2HINT
+                ptx::tma_store_2d_hint(&tm_out.seg[sgm], stage_buf, c_store - sgm * p.seg_cols, m0, stream_out);
+#else
                 ptx::tma_store_2d(&tm_out.seg[sgm], stage_buf, c_store - sgm * p.seg_cols, m0);
+#endif
               } else {
+#if B200W4A4_OPT_L2HINT
+                ptx::tma_store_2d_hint(&tm_out.seg[0], stage_buf, c_store, m0, stream_out);
+#else
                 ptx::tma_store_2d(&tm_out.seg[0], stage_buf, c_store, m0);
+#endif
               }
             }
             ptx::tma_store_commit();

@@ -11,9 +11,9 @@
 //   amax  = max_k |x[m,k]|
 //   s[m]  = (max(amax, 1e-5f) / 7.0f) * clip
 //   q     = clamp(rint(x / s[m]), -8, 7)            (true division, ties to even)
-// The kernel evaluates q with a reciprocal multiply and falls back to the division for
-// values near a rounding tie, which provably yields the same integer (see chunk_codes).
-// which is UniformQuantizer's symmetric path on an fp32 2-D input
+// The kernel evaluates q with two fused multiply-adds per value and falls back to the division
+// for values near a rounding tie, which provably yields the same integer (see chunk_codes).
+// This is UniformQuantizer's symmetric path on an fp32 2-D input
 // (vdm_infer/quantization/quant_linear.py:43-48, :64-66) with the clip applied
 // to the scale as the kernel path does (vdm_w4a4_kernel.cu:478).
 #pragma once
@@ -141,27 +141,38 @@ __device__ __forceinline__ uint32_t code_bits_div(float x, float s) {
   return __float_as_uint(t + kRoundMagic);
 }
 
-// Eight codes of one chunk.  Fast path: t = x * r with r = RN(1/s) instead of the division.
-// |t - x/s| <= |x/s| * 2^-23 < 2^-19 in the unclamped range, so rint(t) can differ from
-// rint(fl(x/s)) only if t lies within 2^-18 of a half-integer; such chunks (about one in
-// ten thousand) are redone with the IEEE division, which makes the result identical to
-// clamp(rint(x / s)) for every input.  `exact_only` rows (scale so large that 1/s would be
-// subnormal) always take the division.
-__device__ __forceinline__ void chunk_codes(const float (&v)[8], float s, float r, bool exact_only,
-                                            uint32_t (&c)[8]) {
-  float worst = 0.0f;
+// Per-row constants of the fast path.
+struct RowQuant {
+  float s;          // scale
+  float r_up, r_dn; // RN(1/s) nudged up / down by 2^-20: brackets of the true reciprocal
+  bool exact_only;  // scale so large or small that 1/s is not a normal number: always divide
+  bool clamp;       // |x/s| can exceed 7.5 (clip below ~0.934): clamp the rounded values
+};
+
+// Eight codes of one chunk.  Fast path: two fused multiply-adds per value,
+//   ya = RN(x * r_up + magic),  yb = RN(x * r_dn + magic),
+// each a single rounding of the exact product to an integer (ties to even, like rint).  The
+// products bracket both the true quotient and its fp32 rounding fl(x/s), because r_up / r_dn
+// differ from 1/s by at least 2^-21 relative while RN(1/s) and fl(x/s) are off by at most 2^-24
+// each; rint is monotonic, so ya == yb implies rint(fl(x/s)) == ya.  When they differ somewhere
+// in the chunk (a value within ~2^-16 of a rounding tie: a few chunks per hundred thousand) the
+// chunk is redone with the IEEE division, so the result equals clamp(rint(x / s)) for every input.
+__device__ __forceinline__ void chunk_codes(const float (&v)[8], const RowQuant& rq, uint32_t (&c)[8]) {
+  uint32_t diff = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float t = __fmul_rn(v[i], r);
-    t = fminf(fmaxf(t, -8.0f), 7.0f);
-    const float y = __fadd_rn(t, kRoundMagic);
-    const float d = __fsub_rn(t, __fsub_rn(y, kRoundMagic));  // exact distance to the chosen integer
-    worst = fmaxf(worst, fabsf(d));
-    c[i] = __float_as_uint(y);
+    float ya = __fmaf_rn(v[i], rq.r_up, kRoundMagic);
+    float yb = __fmaf_rn(v[i], rq.r_dn, kRoundMagic);
+    if (rq.clamp) {
+      ya = fminf(fmaxf(ya, kRoundMagic - 8.0f), kRoundMagic + 7.0f);
+      yb = fminf(fmaxf(yb, kRoundMagic - 8.0f), kRoundMagic + 7.0f);
+    }
+    diff |= __float_as_uint(ya) ^ __float_as_uint(yb);
+    c[i] = __float_as_uint(ya);
   }
-  if (exact_only || worst >= 0.5f - 3.814697265625e-06f) {  // 2^-18
+  if (rq.exact_only || diff != 0) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = code_bits_div(v[i], s);
+    for (int i = 0; i < 8; ++i) c[i] = code_bits_div(v[i], rq.s);
   }
 }
 
@@ -182,10 +193,16 @@ __device__ __forceinline__ void store_codes(void* q, size_t row, int K, int chun
   }
 }
 
-// Reciprocal used by the fast path, and whether the row must use the division throughout.
-__device__ __forceinline__ float scale_reciprocal(float s, bool& exact_only) {
-  exact_only = !(s < 1.0e30f);  // also true for NaN / inf scales
-  return exact_only ? 0.0f : __frcp_rn(s);
+__device__ __forceinline__ RowQuant row_quant(float amax, float clip) {
+  RowQuant rq;
+  rq.s = row_scale(amax, clip);
+  rq.exact_only = !(rq.s < 1.0e30f) || !(rq.s > 1.0e-30f);  // also true for NaN / inf scales
+  const float r = rq.exact_only ? 0.0f : __frcp_rn(rq.s);
+  rq.r_up = __fmul_rn(r, 1.0f + 9.5367431640625e-07f);  // 1 + 2^-20
+  rq.r_dn = __fmul_rn(r, 1.0f - 9.5367431640625e-07f);
+  // |x| <= amax gives |x/s| <= 7/clip; rounding stays within [-7, 7] while that is below 7.5.
+  rq.clamp = !(clip >= 0.934f);
+  return rq;
 }
 
 }  // namespace detail
@@ -230,10 +247,8 @@ quant_act_rows_kernel(const T* __restrict__ x, void* __restrict__ q, float* __re
     for (int w = 1; w < WPR; ++w) amax = fmaxf(amax, wmax[w0 + w]);
   }
   if (!row_ok) return;
-  const float s = detail::row_scale(amax, clip);
-  bool exact_only;
-  const float r = detail::scale_reciprocal(s, exact_only);
-  if (t == 0) scale[row] = s;
+  const detail::RowQuant rq = detail::row_quant(amax, clip);
+  if (t == 0) scale[row] = rq.s;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
@@ -241,7 +256,7 @@ quant_act_rows_kernel(const T* __restrict__ x, void* __restrict__ q, float* __re
       float v[8];
       uint32_t codes[8];
       ch[i].values(v);
-      detail::chunk_codes(v, s, r, exact_only, codes);
+      detail::chunk_codes(v, rq, codes);
       detail::store_codes<QOUT>(q, static_cast<size_t>(row), K, c, codes);
     }
   }
@@ -356,10 +371,8 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
   }
   amax = row_reduce<TPR, true>(amax, red[2], sub);
   if (!row_ok) return;
-  const float s = detail::row_scale(amax, clip);
-  bool exact_only;
-  const float r = detail::scale_reciprocal(s, exact_only);
-  if (t == 0) scale[row] = s;
+  const detail::RowQuant rq = detail::row_quant(amax, clip);
+  if (t == 0) scale[row] = rq.s;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
@@ -367,7 +380,7 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
       float v[8];
       uint32_t codes[8];
       transformed(i, c, v);
-      detail::chunk_codes(v, s, r, exact_only, codes);
+      detail::chunk_codes(v, rq, codes);
       detail::store_codes<QOUT_INT8>(q, static_cast<size_t>(row), K, c, codes);
     }
   }
@@ -396,17 +409,15 @@ quant_act_long_rows_kernel(const T* __restrict__ x, void* __restrict__ q,
   amax = wmax[0];
 #pragma unroll
   for (int w = 1; w < 8; ++w) amax = fmaxf(amax, wmax[w]);
-  const float s = detail::row_scale(amax, clip);
-  bool exact_only;
-  const float r = detail::scale_reciprocal(s, exact_only);
-  if (threadIdx.x == 0) scale[row] = s;
+  const detail::RowQuant rq = detail::row_quant(amax, clip);
+  if (threadIdx.x == 0) scale[row] = rq.s;
   for (int c = threadIdx.x; c < nchunks; c += 256) {
     detail::Chunk<T> ch;
     float v[8];
     uint32_t codes[8];
     ch.load(xr + 8 * c);
     ch.values(v);
-    detail::chunk_codes(v, s, r, exact_only, codes);
+    detail::chunk_codes(v, rq, codes);
     detail::store_codes<QOUT>(q, static_cast<size_t>(row), K, c, codes);
   }
 }

@@ -439,6 +439,20 @@ def last_device_status(device: Optional[int] = None) -> int:
     return _load_ext().b200w4a4_last_device_status(idx)
 
 
+def check_device(device: Optional[int] = None) -> None:
+    """Synchronises the device and raises B200W4A4Error (code B200W4A4_EDEVICE) if a kernel has
+    recorded a time-out since the status word was last cleared; the word is left in place."""
+    idx = torch.cuda.current_device() if device is None else int(device)
+    _lib.check(_load_ext().b200w4a4_check_device(idx), "check_device")
+
+
+def map_cache_stats() -> Tuple[int, int]:
+    """(hits, misses) of the library's tensor-map table since it was loaded."""
+    h, m = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    _load_ext().b200w4a4_map_cache_stats(ctypes.byref(h), ctypes.byref(m))
+    return int(h.value), int(m.value)
+
+
 # --------------------------------------------------------------------------- fused variants
 _PROLOGUES = {None: 0, "none": 0, "gelu_tanh": 1, "layernorm_mod": 2}
 _EPILOGUES = {None: 0, "none": 0, "gelu_tanh": 1, "gate_residual": 2}

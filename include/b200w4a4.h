@@ -247,8 +247,24 @@ int b200w4a4_unpack_codes(const void* packed, int8_t* codes, int rows, int K, in
 int b200w4a4_set_cta_group(int cta_group);
 
 /* Synchronises `device`, returns and clears its device status word:
- * 0, or the code (> 0) of the kernel role whose bounded wait ran out. */
+ * 0, or the code (> 0) of the kernel role whose bounded wait ran out
+ * (101-104: a role of the GEMM; 105: b200w4a4_wait_flags).  The word is a report
+ * only: it keeps the first code until it is read here and never cancels a later
+ * launch (a GEMM gives up early only on a time-out of its own launch).
+ * No counterpart in the reference, whose kernels have no waits to bound. */
 int b200w4a4_last_device_status(int device);
+
+/* Synchronises `device` and returns B200W4A4_OK, or B200W4A4_EDEVICE when a kernel
+ * has recorded a time-out since the word was last cleared (the word is left as it
+ * is, so b200w4a4_last_device_status still tells which role).  The reference
+ * surfaces device-side failures through TORCH_CHECK / cudaGetLastError after its
+ * launches (vdm_w4a4_kernel.cu:700-728, 765-838); this is the explicit form. */
+int b200w4a4_check_device(int device);
+
+/* Tensor-map table statistics: launches whose TMA descriptors were found in the
+ * library's table (hits) or had to be encoded by the driver (misses).  Either
+ * pointer may be NULL.  No counterpart in the reference (it uses no TMA). */
+void b200w4a4_map_cache_stats(unsigned long long* hits, unsigned long long* misses);
 
 #ifdef __cplusplus
 }

@@ -160,3 +160,39 @@ def test_exchange_reports_a_missing_peer(mods):
     assert vdm.last_device_status() == 105
     with pytest.raises(ValueError):
         ex0.push("k", torch.zeros(600, D, device="cuda").half(), None, None, 1e-6, 128)
+
+
+def test_unread_timeout_does_not_cancel_later_gemms(mods):
+    """The status word is a report, not a kill switch: a wait_flags time-out that the host has not
+    read yet must not make a later GEMM drain early.  The GEMM stays bit-exact, check_device
+    answers EDEVICE, and the code is still there to be read (and cleared) afterwards."""
+    import numpy as np
+
+    from _cases import make_case
+    from dsaquant_b200 import _lib
+    from oracle import w4a4_oracle as orc
+
+    aq, vdm = mods
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    aq.wait_flags(flags, 5, timeout_ms=30)            # nothing ever sets these flags
+    torch.cuda.synchronize()                          # the time-out is recorded, and deliberately not read
+
+    M, K, N = 3000, 1536, 1536                        # 72 tiles of 12 k-blocks: many barrier waits that spin
+    x16, w16, b16 = make_case(77, M, K, N)
+    ws = orc.weight_scale_absmax(w16)
+    qw = orc.quantize_weight(w16, ws)
+    qweight = torch.from_numpy(orc.pack_weight_v1(qw)).cuda()
+    wscales = torch.from_numpy(orc.pack_wscale_v1(ws, K)).cuda()
+    for cg in (2, 1):
+        prev = vdm.set_cta_group(cg)
+        try:
+            out = vdm.linear_vdm_w4a4(torch.from_numpy(x16).cuda(), qweight, wscales, torch.from_numpy(b16).cuda(), 0.95)
+        finally:
+            vdm.set_cta_group(prev)
+        ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)
+        np.testing.assert_array_equal(out.cpu().numpy().view(np.uint16), ref["out"].view(np.uint16))
+    with pytest.raises(_lib.B200W4A4Error) as err:
+        vdm.check_device()
+    assert err.value.code == -7
+    assert vdm.last_device_status() == 105            # still readable, cleared by this read
+    vdm.check_device()                                # clean again

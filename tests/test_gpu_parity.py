@@ -38,7 +38,7 @@ def _v1_buffers(w16, ws16):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,K", [(1, 64), (15, 128), (257, 1536), (33, 3072), (40, 5120), (9, 8960),
                                  (5, 13824), (3, 16448)])
-@pytest.mark.parametrize("clip", [1.0, 0.95])
+@pytest.mark.parametrize("clip", [1.0, 0.95, 0.5])   # 0.5: quotients beyond +-7.5, the clamping path
 def test_quantize_act_codes_bit_exact(vdm, dtype, M, K, clip):
     x16, _, _ = make_case(100 + M + K, M, K, 128, bias=False)
     xt = _cuda(x16).to(dtype)                       # exact for fp32; bf16 rounds: oracle sees the same values
@@ -206,3 +206,29 @@ def test_random_shape_sweep_bit_exact(vdm):
             _gemm_case(vdm, M, K, N, seed=3000 + i, clip=clip, bias=bias)
         finally:
             vdm.set_cta_group(prev)
+
+
+def test_tensor_maps_are_reused_between_identical_launches(vdm):
+    """Second launch with the same buffers finds all three TMA descriptors in the library's table."""
+    x16, w16, _ = make_case(5, 300, 256, 256, bias=False)
+    ws = orc.weight_scale_absmax(w16)
+    qw, qweight, wscales = _v1_buffers(w16, ws)
+    qact, ascales, _ = vdm.quantize_activation_per_token(_cuda(x16), 1.0)
+    lib = __import__("dsaquant_b200")._lib.load()
+    w_b200, w_scale = vdm.prepare_b200_weight(qweight, wscales)
+    out = torch.empty(300, 256, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        rc = lib.b200w4a4_gemm(qact.data_ptr(), ascales.data_ptr(), w_b200.data_ptr(), w_scale.data_ptr(), None,
+                               out.data_ptr(), None, 300, 256, 256, s)
+        assert rc == 0
+
+    launch()
+    h0, m0 = vdm.map_cache_stats()
+    first = out.clone()
+    launch()
+    h1, m1 = vdm.map_cache_stats()
+    assert (h1 - h0, m1 - m0) == (3, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out, first)

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
 
     header = (ROOT / "include" / "b200w4a4.h").read_text()
     declared = set(re.findall(r"\b(b200w4a4_[a-z0-9_]+)\s*\(", header))
-    assert len(declared) == 25
+    assert len(declared) == 27
     lib = _lib.load()
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
@@ -372,3 +372,41 @@ def test_public_header_is_plain_c(tmp_path):
                    check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0 and out.stdout.startswith("1 unsupported shape")
+
+
+def test_quantiser_fast_path_bracket_is_exact():
+    """CPU emulation of the quantiser's fast path (dsaquant_b200/csrc/quant_act.cuh, chunk_codes):
+    two fused multiply-adds with the reciprocal nudged up / down by 2^-20 must agree whenever the
+    pinned definition clamp(rint(x / s)) is not within reach of a rounding tie, and when they agree
+    they must equal it.  fp64 holds the product of two fp32 numbers exactly, and adding the 1.5*2^23
+    constant in one rounding is rint() of that exact product, so numpy reproduces the GPU bits."""
+    import numpy as np
+
+    rng = np.random.default_rng(5)
+    one_up, one_dn = np.float32(1.0 + 2.0 ** -20), np.float32(1.0 - 2.0 ** -20)
+    checked = 0
+    for clip in (1.0, 0.95, 0.934, 0.5):
+        amax = np.abs(rng.standard_normal(4000).astype(np.float16).astype(np.float32)) * np.float32(30.0) + np.float32(1e-3)
+        s = ((np.maximum(amax, np.float32(1e-5)) / np.float32(7.0)) * np.float32(clip)).astype(np.float32)
+        r = (np.float32(1.0) / s).astype(np.float32)
+        r_up, r_dn = (r * one_up).astype(np.float32), (r * one_dn).astype(np.float32)
+        # values spread over [-amax, amax] plus neighbours of every half-integer multiple of s
+        u = (rng.uniform(-1, 1, (4000, 256)).astype(np.float32) * amax[:, None]).astype(np.float16).astype(np.float32)
+        ties = (np.arange(-15, 16, 2, dtype=np.float32) * np.float32(0.5))[None, :] * s[:, None]
+        near = np.concatenate([np.nextafter(ties, np.float32(np.inf)), ties, np.nextafter(ties, np.float32(-np.inf)),
+                               ties.astype(np.float16).astype(np.float32)], axis=1)
+        near = np.clip(near, -amax[:, None], amax[:, None]).astype(np.float32)
+        x = np.concatenate([u, near], axis=1)
+        want = np.clip(np.rint((x / s[:, None]).astype(np.float32)), -8, 7)
+        ya = np.rint(x.astype(np.float64) * r_up[:, None].astype(np.float64))
+        yb = np.rint(x.astype(np.float64) * r_dn[:, None].astype(np.float64))
+        if not clip >= 0.934:
+            ya, yb = np.clip(ya, -8, 7), np.clip(yb, -8, 7)
+        agree = ya == yb
+        assert np.array_equal(ya[agree], want[agree])
+        assert agree[:, :256].mean() > 0.9999           # on ordinary values the division fallback stays rare
+        assert not agree[:, 256:].all()                 # and the planted ties do reach it
+        if clip >= 0.934:
+            assert np.abs(ya).max() <= 7                # no clamp needed on this path
+        checked += x.size
+    assert checked > 4_000_000

@@ -56,6 +56,35 @@ def test_noalloc_entry_matches_workspace_entry_twice():
         ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)
         np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), ref["out"].view(np.uint16))
 
+    # Exactly at both limits (rows = max_rows, codes = max_codes): the last code byte sits next to
+    # the first scale and the whole scale region is in use.  Issued on a second stream after a
+    # device synchronisation, which is all the ordering the shared scratch asks for.
+    M, K, N = max_rows, max_codes // max_rows, 128
+    x16, w16, b16 = make_case(43, M, K, N)
+    ws = orc.weight_scale_absmax(w16)
+    qw = orc.quantize_weight(w16, ws)
+    x = torch.from_numpy(x16).to(dev)
+    w_b200 = torch.from_numpy(orc.repack_b200(qw)).to(dev)
+    w_scale = torch.from_numpy(ws).to(dev)
+    bias = torch.from_numpy(b16).to(dev)
+    ws_bytes = lib.b200w4a4_linear_workspace_bytes(M, K)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    want = torch.empty(M, N, dtype=torch.float16, device=dev)
+    got = torch.full((M, N), float("nan"), dtype=torch.float16, device=dev)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    side_ptr = ctypes.c_void_p(side.cuda_stream)
+    rc = lib.b200w4a4_linear(_ptr(x), 0, _ptr(w_b200), _ptr(w_scale), _ptr(bias), _ptr(want),
+                             _ptr(workspace), ws_bytes, M, N, K, 0.95, side_ptr)
+    assert rc == 0, _lib.strerror(rc)
+    rc = lib.b200w4a4_linear_noalloc(_ptr(x), 0, _ptr(w_b200), _ptr(w_scale), _ptr(bias), _ptr(got),
+                                     M, N, K, 0.95, side_ptr)
+    assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
+    ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)
+    np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), ref["out"].view(np.uint16))
+
     # Sizes beyond the built-in scratch are refused with a clear error and launch nothing.
     out = torch.empty(8, dtype=torch.float16, device=dev)
     rc = lib.b200w4a4_linear_noalloc(_ptr(x), 0, _ptr(w_b200), _ptr(w_scale), None, _ptr(out),
