@@ -36,7 +36,7 @@
 #define B200W4A4_OPT_L2HINT 1
 #endif
 #ifndef B200W4A4_OPT_FENCE_KB0
-#define B200W4A4_OPT_FENCE_KB0 0
+#define B200W4A4_OPT_FENCE_KB0 1
 #endif
 #ifndef B200W4A4_ABL_W8
 #define B200W4A4_ABL_W8 0

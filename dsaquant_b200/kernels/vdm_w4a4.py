@@ -227,6 +227,16 @@ def _pack(lib, weight_h: torch.Tensor, scale_h: Optional[torch.Tensor]):
 
 _PREPARED: dict = {}
 
+# Optional profiling hook: when set, it is called with "quant" right before an activation
+# quantiser is enqueued and with "gemm" right before a GEMM (a benchmark records CUDA events
+# there).  None in normal use: the calls below then cost one comparison.
+_PHASE_HOOK = None
+
+
+def set_phase_hook(fn) -> None:
+    global _PHASE_HOOK
+    _PHASE_HOOK = fn
+
 
 def _version_of(t: torch.Tensor) -> int:
     try:
@@ -531,16 +541,28 @@ def linear_vdm_w4a4_fused(
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     if m == 0:
         return out.view(*orig_shape, n)
-    if x_2d.dtype != torch.float16:
-        # bf16 / fp32 activations (e.g. the attention output): quantised from their exact values,
-        # then the GEMM with the fused epilogue.
+    hook = _PHASE_HOOK
+    if x_2d.dtype != torch.float16 or hook is not None:
+        # bf16 / fp32 activations (e.g. the attention output) are quantised from their exact
+        # values, then the GEMM with the fused epilogue runs: two library calls.  A profiling
+        # hook takes the same route so that it can put a mark between the two kernels.
         qact = torch.empty((m, k), dtype=torch.int8, device=dev)
         act_scale = torch.empty((m,), dtype=torch.float32, device=dev)
         with _DeviceGuard(dev):
             stream = _stream_ptr(dev)
-            rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], qact.data_ptr(), 0,
-                                           act_scale.data_ptr(), m, k, float(clip_ratio), stream)
+            if hook is not None:
+                hook("quant")
+            if pre == 0:
+                rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], qact.data_ptr(), 0,
+                                               act_scale.data_ptr(), m, k, float(clip_ratio), stream)
+            else:
+                rc = lib.b200w4a4_quantize_act_fused(
+                    x_2d.data_ptr(), pre, ms.data_ptr() if ms is not None else None,
+                    mh.data_ptr() if mh is not None else None, m_stride, float(ln_eps), qact.data_ptr(),
+                    act_scale.data_ptr(), m, k, float(clip_ratio), stream)
             _lib.check(rc, "quantize_act")
+            if hook is not None:
+                hook("gemm")
             rc = lib.b200w4a4_gemm_fused(
                 qact.data_ptr(), act_scale.data_ptr(), w_b200.data_ptr(), w_scale.data_ptr(),
                 b.data_ptr() if b is not None else None, out.data_ptr(), epi,
@@ -626,6 +648,9 @@ def linear_vdm_w4a4_split(
     lds = (ctypes.c_longlong * segments)(*[(o.stride(0) if m > 1 else seg) for o in outs])
     with _DeviceGuard(dev):
         stream = _stream_ptr(dev)
+        hook = _PHASE_HOOK
+        if hook is not None:
+            hook("quant")
         if pre == 0:
             rc = lib.b200w4a4_quantize_act(x_2d.data_ptr(), _DTYPE_CODE[x_2d.dtype], qact.data_ptr(), 0,
                                            act_scale.data_ptr(), m, k, float(clip_ratio), stream)
@@ -635,6 +660,8 @@ def linear_vdm_w4a4_split(
                 mh.data_ptr() if mh is not None else None, m_stride, float(ln_eps), qact.data_ptr(),
                 act_scale.data_ptr(), m, k, float(clip_ratio), stream)
         _lib.check(rc, "quantize_act")
+        if hook is not None:
+            hook("gemm")
         rc = lib.b200w4a4_gemm_split(qact.data_ptr(), act_scale.data_ptr(), w_b200.data_ptr(),
                                      w_scale.data_ptr(), b.data_ptr() if b is not None else None,
                                      ptrs, lds, segments, m, n, k, stream)

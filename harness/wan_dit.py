@@ -43,6 +43,43 @@ from dsaquant_b200 import sharding
 from dsaquant_b200.attention_qkv import get_qkv_projections
 from dsaquant_b200.quantization.quant_linear import QuantLinear
 
+class PhaseTimer:
+    """Attributes GPU time of one stream to named phases: mark(name) records a CUDA event; the
+    time from one mark to the next belongs to the earlier mark's name.  Used by the benchmark
+    for one extra, untimed step; None otherwise."""
+
+    def __init__(self):
+        self.marks = []
+
+    def mark(self, name: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((name, ev))
+
+    def totals_ms(self) -> dict:
+        out = {}
+        for (name, a), (_, b) in zip(self.marks, self.marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
+PHASES: Optional[PhaseTimer] = None
+
+
+def set_phase_timer(timer: Optional[PhaseTimer]) -> None:
+    """Installs (or removes) the phase timer here and as the library wrapper's quant/gemm hook."""
+    global PHASES
+    from dsaquant_b200.kernels import vdm_w4a4 as vdm
+
+    PHASES = timer
+    vdm.set_phase_hook(None if timer is None else timer.mark)
+
+
+def _mark(name: str) -> None:
+    if PHASES is not None:
+        PHASES.mark(name)
+
+
 QPARAMS = {"w": {"bit": 4, "sym": True, "granularity": "per_channel"}, "act": {"bit": 4, "sym": True}}
 KERNEL_CLIP = 0.95
 
@@ -219,29 +256,37 @@ def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
     cs = None if freqs is None else torch.view_as_real(freqs).reshape(freqs.shape[0], -1)
     gather = group is not None and is_self
     exchange = getattr(attn, "kv_exchange", None) if gather else None
+    _mark("glue")
     if exchange is not None:
         # The kernels that produce K and V store their rows into every rank's gather buffer.
         exchange.begin_block()
         exchange.push("v", v[0], None, None, eps, hd)
         exchange.push("k", k[0], attn.norm_k.weight, cs, eps, hd)
         qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        _mark("exchange_wait")
         kn, vb = exchange.gathered(m_total, attn.kv_senders)
     else:
         vb = qk_norm_rope(v[0], None, None, eps, hd)
         if gather:
             v_work, v_full = sharding.all_gather_rows(vb, m_total, group, async_op=True)
-        qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        # K before Q: its all-gather is asynchronous too and overlaps Q's pass.
         kn = qk_norm_rope(k[0], attn.norm_k.weight, cs, eps, hd)
         if gather:
-            kn = sharding.all_gather_rows(kn, m_total, group)
+            k_work, k_full = sharding.all_gather_rows(kn, m_total, group, async_op=True)
+        qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        if gather:
+            _mark("exchange_wait")
+            k_work.wait()
             v_work.wait()
-            vb = v_full
+            kn, vb = k_full, v_full
+    _mark("sdpa")
     lq, lk = qn.shape[0], kn.shape[0]
     o = F.scaled_dot_product_attention(qn.view(1, lq, heads, hd).transpose(1, 2),
                                        kn.view(1, lk, heads, hd).transpose(1, 2),
                                        vb.view(1, lk, heads, hd).transpose(1, 2), dropout_p=0.0, is_causal=False)
     if exchange is not None:
         exchange.end_block()
+    _mark("other")
     return o.transpose(1, 2).reshape(1, lq, d)
 
 
@@ -384,9 +429,10 @@ class WanDiT(nn.Module):
             blk.fused = bool(on)
 
     # ---- forward ------------------------------------------------------------------------
-    def enable_kv_push(self, group) -> None:
-        """Row-sharded self-attention exchanges K and V through peer memory (one PeerKVExchange shared
-        by all blocks) instead of two all-gathers per block.  Fused kernel route only."""
+    def make_kv_exchange(self, group):
+        """Exchange memory for row-sharded self-attention over `group` (one PeerKVExchange shared by
+        all blocks): K and V travel by peer stores from the kernels that produce them instead of
+        two all-gathers per block.  Collective: every rank of the group must call it."""
         from dsaquant_b200.peer_exchange import PeerKVExchange
 
         world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -394,9 +440,18 @@ class WanDiT(nn.Module):
         parts = sharding.row_partition(m_total, world)
         cap = sharding.shard_capacity(m_total, world) * world
         ex = PeerKVExchange.from_symmetric_memory(group, cap, self.cfg.dim, parts[rank][0])
+        ex.senders = sum(1 for s, e in parts if e > s)
+        return ex
+
+    def set_kv_exchange(self, exchange) -> None:
+        """Route of the K/V exchange: a PeerKVExchange (fused kernel route only), or None for the
+        NCCL all-gathers."""
         for blk in self.blocks:
-            blk.attn1.kv_exchange = ex
-            blk.attn1.kv_senders = sum(1 for s, e in parts if e > s)
+            blk.attn1.kv_exchange = exchange
+            blk.attn1.kv_senders = None if exchange is None else exchange.senders
+
+    def enable_kv_push(self, group) -> None:
+        self.set_kv_exchange(self.make_kv_exchange(group))
 
     def embed_time(self, timestep: torch.Tensor):
         half = self.cfg.freq_dim // 2
@@ -422,6 +477,7 @@ class WanDiT(nn.Module):
         if getattr(self, "_rope_key", None) != key:     # the table depends on the grid only: build it once
             self._rope_key, self._rope = key, rope_table(cfg.dim // cfg.heads, fp, hp, wp, latent.device)
         freqs = self._rope
+        _mark("other")
         if group is not None:
             rank, world = dist.get_rank(group), dist.get_world_size(group)
             s, e = sharding.row_partition(m_total, world)[rank]
@@ -431,6 +487,7 @@ class WanDiT(nn.Module):
         ctx = self.text_embedder(text.to(x.dtype))
         for blk in self.blocks:
             x = blk(x, ctx, temb6, freqs, group, m_total)
+        _mark("other")
         mod = self.scale_shift_table.float() + temb.float()[:, None]
         shift, scale = mod[:, 0][None], mod[:, 1][None]
         x = (fp32_layer_norm(x, cfg.eps) * (1 + scale) + shift).to(x.dtype)
@@ -438,6 +495,7 @@ class WanDiT(nn.Module):
         if group is not None:
             x = sharding.all_gather_rows(x[0].contiguous(), m_total, group)[None]
         n = math.prod(cfg.patch)
+        _mark("end")
         return x.reshape(1, m_total, n, -1).reshape(1, m_total * n, -1)
 
 

@@ -1,7 +1,7 @@
 """Builds the REFERENCE's own CUDA extension for sm_100a as a checker / same-box GPU baseline.
 
 TEST / BASELINE INFRASTRUCTURE.  Compiles vdm_infer/kernels/csrc/vdm_w4a4_kernel.cu from the
-reference checkout where it lies (its location is taken from DSAQUANT_REFERENCE)
+reference checkout where it lies (DSAQUANT_REFERENCE, or a `reference` directory beside this repository)
 with the reference's own flags (-O3 --use_fast_math -lineinfo, vdm_w4a4.py:151-162) into
 oracle/_ref/vdm_w4a4_ref_ext.so (git-ignored; no reference source is copied).  The module is a
 pybind11 torch extension: import it with oracle._ref_loader.load().  It is used only by tests
@@ -22,8 +22,20 @@ OUT = HERE / "_ref" / "vdm_w4a4_ref_ext.so"
 NAME = "vdm_w4a4_ref_ext"
 
 
+def reference_checkout() -> Path | None:
+    """The DSAQuant checkout: the directory DSAQUANT_REFERENCE names, else a directory called
+    `reference` next to this repository; None when neither holds the kernel source."""
+    cands = [os.environ.get("DSAQUANT_REFERENCE"), str(HERE.parent.parent / "reference")]
+    for c in cands:
+        if c and (Path(c) / "vdm_infer" / "kernels" / "csrc" / "vdm_w4a4_kernel.cu").exists():
+            return Path(c)
+    return None
+
+
 def build(force: bool = False) -> Path | None:
-    ref = Path(os.environ.get("DSAQUANT_REFERENCE", "/root/reference"))
+    ref = reference_checkout()
+    if ref is None:
+        return OUT if OUT.exists() else None
     src = ref / "vdm_infer" / "kernels" / "csrc" / "vdm_w4a4_kernel.cu"
     if not src.exists():
         return OUT if OUT.exists() else None

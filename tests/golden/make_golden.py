@@ -1,7 +1,7 @@
 """Regenerates tests/golden/*.npz by running the REFERENCE's own PyTorch W4A4 path.
 
-Run in a container that has the reference checkout (location: DSAQUANT_REFERENCE,
-or the default in the code below):
+Run where a DSAQuant checkout exists (DSAQUANT_REFERENCE, or a directory called
+`reference` next to this repository):
 
     python tests/golden/make_golden.py
 
@@ -28,7 +28,10 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
-sys.path.insert(0, os.environ.get("DSAQUANT_REFERENCE", "/root/reference"))
+_REF = os.environ.get("DSAQUANT_REFERENCE") or str(HERE.parent.parent.parent / "reference")
+if not (Path(_REF) / "vdm_infer").is_dir():
+    raise SystemExit("set DSAQUANT_REFERENCE to a DSAQuant checkout (or place one next to this repository)")
+sys.path.insert(0, _REF)
 
 from _cases import CASES, digest, make_case  # noqa: E402
 from vdm_infer.quantization.quant_linear import QuantLinear  # noqa: E402  (reference code)
