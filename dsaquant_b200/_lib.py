@@ -40,6 +40,7 @@ SIGNATURES = {
     "b200w4a4_linear_noalloc_max_rows": (c_int, []),
     "b200w4a4_unpack_codes": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200w4a4_set_cta_group": (c_int, [c_int]),
+    "b200w4a4_set_weight_staging": (c_int, [c_int]),
     "b200w4a4_last_device_status": (c_int, [c_int]),
     "b200w4a4_check_device": (c_int, [c_int]),
     "b200w4a4_map_cache_stats": (None, [POINTER(ctypes.c_ulonglong), POINTER(ctypes.c_ulonglong)]),

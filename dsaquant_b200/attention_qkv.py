@@ -20,11 +20,25 @@ from .kernels.vdm_w4a4 import linear_vdm_w4a4, linear_vdm_w4a4_qkv
 
 
 def _cat_cached(attn, prefix: str, layers) -> None:
+    """Builds (once) the concatenated v1 weight / scale / bias caches of a fused projection under
+    the attribute names the reference uses.  The member layers then stop holding copies of their
+    own: their `vdm_weight_packed` / `vdm_weight_scale_packed` buffers become row views of the
+    concatenated tensors (same bytes, still saved per layer by a state dict), and the per-layer
+    repacked weights, which the fused path never reads, are dropped from the repack table."""
     if getattr(attn, f"{prefix}_weight_packed", None) is None:
-        setattr(attn, f"{prefix}_weight_packed",
-                torch.cat([l.vdm_weight_packed for l in layers], dim=0).contiguous())
-        setattr(attn, f"{prefix}_weight_scale",
-                torch.cat([l.vdm_weight_scale_packed for l in layers], dim=0).contiguous())
+        from .kernels.vdm_w4a4 import release_b200_weight
+
+        packed = torch.cat([l.vdm_weight_packed for l in layers], dim=0).contiguous()
+        scale = torch.cat([l.vdm_weight_scale_packed for l in layers], dim=0).contiguous()
+        setattr(attn, f"{prefix}_weight_packed", packed)
+        setattr(attn, f"{prefix}_weight_scale", scale)
+        row = 0
+        for l in layers:
+            n = l.vdm_weight_packed.shape[0]
+            release_b200_weight(l.vdm_weight_packed)
+            l._buffers["vdm_weight_packed"] = packed[row:row + n]
+            l._buffers["vdm_weight_scale_packed"] = scale[row:row + n]
+            row += n
     if not hasattr(attn, f"{prefix}_bias_half") or getattr(attn, f"{prefix}_bias_half") is None:
         n = layers[0].vdm_weight_packed.shape[0]
         if any(l._bias_half is not None for l in layers):
@@ -34,6 +48,21 @@ def _cat_cached(attn, prefix: str, layers) -> None:
             setattr(attn, f"{prefix}_bias_half", torch.cat(parts, dim=0).contiguous())
         else:
             setattr(attn, f"{prefix}_bias_half", None)
+
+
+def prepare_fused_projections(attn) -> None:
+    """What the first fused forward would do, done ahead of time: concatenate the members'
+    buffers and (on a CUDA device) repack the concatenated weight for the GEMM."""
+    from .kernels.vdm_w4a4 import prepare_b200_weight
+
+    if attn.cross_attention_dim_head is None:
+        prefix, layers = "_vdm_qkv", (attn.to_q, attn.to_k, attn.to_v)
+    else:
+        prefix, layers = "_vdm_kv", (attn.to_k, attn.to_v)
+    _cat_cached(attn, prefix, layers)
+    packed = getattr(attn, f"{prefix}_weight_packed")
+    if packed.is_cuda:
+        prepare_b200_weight(packed, getattr(attn, f"{prefix}_weight_scale"))
 
 
 def get_qkv_projections(attn, hidden_states: torch.Tensor, encoder_hidden_states: torch.Tensor):

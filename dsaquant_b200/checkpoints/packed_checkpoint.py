@@ -179,6 +179,12 @@ def enable_fused_qkv(model: nn.Module, *, quant_linear_cls: type[nn.Module],
         if isinstance(attn, attention_cls) and ready(attn.to_q) and ready(attn.to_k) and ready(attn.to_v):
             attn.use_fused_qkv_kernel = True
             attn.qkv_kernel_backend = "vdm"
+            if hasattr(attn, "cross_attention_dim_head"):
+                # Build the concatenated buffers now, so that the member layers' own copies and
+                # per-layer repacks are released at load time instead of at the first forward.
+                from dsaquant_b200.attention_qkv import prepare_fused_projections
+
+                prepare_fused_projections(attn)
 
 
 # ----------------------------------------------------------------------------- writer

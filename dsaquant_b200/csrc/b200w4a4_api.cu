@@ -33,6 +33,7 @@ __device__ int g_device_status;
 __device__ unsigned g_gemm_abort;
 
 std::atomic<int> g_cta_group{0};  // 0 = not chosen yet (environment decides on first use)
+std::atomic<int> g_weight_staging{0};  // 0 = not chosen yet; 4 = packed int4 (default), 8 = int8
 
 struct DeviceState {
   std::once_flag once;
@@ -66,8 +67,10 @@ EncodeTiledFn get_encode() {
 
 template <int CG, int EPI>
 bool set_gemm_smem() {
-  return cudaFuncSetAttribute(gemm_w4a4_kernel<CG, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              GemmCfg<CG>::SMEM_ALLOC) == cudaSuccess;
+  return cudaFuncSetAttribute(gemm_w4a4_kernel<CG, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmCfg<CG, false>::SMEM_ALLOC) == cudaSuccess &&
+         cudaFuncSetAttribute(gemm_w4a4_kernel<CG, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GemmCfg<CG, true>::SMEM_ALLOC) == cudaSuccess;
 }
 
 // Per-device one-time set-up with that device current: capability check, SM
@@ -119,6 +122,16 @@ int current_cta_group() {
     const char* e = getenv("B200W4A4_CTA_GROUP");
     g = (e != nullptr && e[0] == '1') ? 1 : 2;  // the CTA-pair kernel is the default
     g_cta_group.store(g, std::memory_order_relaxed);
+  }
+  return g;
+}
+
+int current_weight_staging() {
+  int g = g_weight_staging.load(std::memory_order_relaxed);
+  if (g == 0) {
+    const char* e = getenv("B200W4A4_WEIGHT_STAGING");
+    g = (e != nullptr && (e[0] == '8' || strcmp(e, "int8") == 0)) ? 8 : 4;  // packed int4 is the default
+    g_weight_staging.store(g, std::memory_order_relaxed);
   }
   return g;
 }
@@ -207,26 +220,26 @@ struct EpiArgs {
   long long seg_ld[3] = {0, 0, 0};
 };
 
-template <int CG, int EPI = EPI_NONE>
-int launch_gemm(DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
+template <int CG, int EPI, bool W8>
+int launch_gemm_staged(DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
                 const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
-                int N, int K, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
-  using C = GemmCfg<CG>;
+                int N, int K, cudaStream_t stream, const EpiArgs& epi) {
+  using C = GemmCfg<CG, W8>;
   CUtensorMap tm_a, tm_w;
   OutMaps tm_out;
   int rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, qact, static_cast<uint64_t>(K),
                      static_cast<uint64_t>(M), static_cast<uint64_t>(K), C::BK, C::BM,
                      CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200W4A4_OK) return rc;
-#if B200W4A4_ABL_W8
-  rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K),
-                 static_cast<uint64_t>(N), static_cast<uint64_t>(K), C::BK, C::B_ROWS,
-                 CU_TENSOR_MAP_SWIZZLE_128B);
-#else
-  rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K / 2),
-                 static_cast<uint64_t>(N), static_cast<uint64_t>(K / 2), C::BK / 2, C::B_ROWS,
-                 CU_TENSOR_MAP_SWIZZLE_NONE);
-#endif
+  if constexpr (W8) {
+    rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K),
+                   static_cast<uint64_t>(N), static_cast<uint64_t>(K), C::BK, C::B_ROWS,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    rc = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w_b200, static_cast<uint64_t>(K / 2),
+                   static_cast<uint64_t>(N), static_cast<uint64_t>(K / 2), C::BK / 2, C::B_ROWS,
+                   CU_TENSOR_MAP_SWIZZLE_NONE);
+  }
   if (rc != B200W4A4_OK) return rc;
   if constexpr (EPI == EPI_SPLIT) {
     const int seg_cols = N / epi.segments;
@@ -281,8 +294,19 @@ int launch_gemm(DeviceState& st, const void* qact, const float* act_scale, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<CG, EPI>, tm_a, tm_w, tm_out, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<CG, EPI, W8>, tm_a, tm_w, tm_out, p);
   return e == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
+template <int CG, int EPI = EPI_NONE>
+int launch_gemm(DeviceState& st, const void* qact, const float* act_scale, const void* w_b200,
+                const __half* w_scale, const __half* bias, __half* out, int32_t* acc_dump, int M,
+                int N, int K, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
+  if (current_weight_staging() == 8)
+    return launch_gemm_staged<CG, EPI, true>(st, qact, act_scale, w_b200, w_scale, bias, out, acc_dump, M, N, K,
+                                             stream, epi);
+  return launch_gemm_staged<CG, EPI, false>(st, qact, act_scale, w_b200, w_scale, bias, out, acc_dump, M, N, K,
+                                            stream, epi);
 }
 
 // ---- scratch of b200w4a4_linear_noalloc -------------------------------------------------
@@ -382,7 +406,7 @@ int b200w4a4_pack_weight(const void* w_f16, const void* ch_scale_f16, void* vdm_
 
 size_t b200w4a4_repack_bytes(int N, int K) {
   if (check_nk(N, K) != B200W4A4_OK) return 0;
-  return static_cast<size_t>(N) * (K / 2);
+  return current_weight_staging() == 8 ? static_cast<size_t>(N) * K : static_cast<size_t>(N) * (K / 2);
 }
 
 int b200w4a4_repack_weight(const void* vdm_packed, void* w_b200, const void* vdm_scale_packed,
@@ -395,9 +419,15 @@ int b200w4a4_repack_weight(const void* vdm_packed, void* w_b200, const void* vdm
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != B200W4A4_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t chunks = static_cast<size_t>(N) * (K / 32);
-  repack_v1_to_b200_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, s>>>(
-      static_cast<const uint32_t*>(vdm_packed), static_cast<uint4*>(w_b200), N, K);
+  if (current_weight_staging() == 8) {
+    const size_t words = static_cast<size_t>(N) * (K / 8);
+    expand_v1_to_int8_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, s>>>(
+        static_cast<const uint32_t*>(vdm_packed), static_cast<uint2*>(w_b200), N, K);
+  } else {
+    const size_t chunks = static_cast<size_t>(N) * (K / 32);
+    repack_v1_to_b200_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, s>>>(
+        static_cast<const uint32_t*>(vdm_packed), static_cast<uint4*>(w_b200), N, K);
+  }
   if (vdm_scale_packed != nullptr) {
     unswizzle_wscale_v1_kernel<<<static_cast<unsigned>((N + 255) / 256), 256, 0, s>>>(
         static_cast<const __half*>(vdm_scale_packed), static_cast<__half*>(w_scale_plain), N, K);
@@ -745,8 +775,11 @@ int b200w4a4_unpack_codes(const void* packed, int8_t* codes, int rows, int K, in
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
   switch (which) {
     case B200W4A4_CODES_WEIGHT_B200:
-      unpack_b200_weight_kernel<<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(packed), codes,
-                                                     rows, K);
+      if (current_weight_staging() == 8)
+        unpack_int8_weight_kernel<<<grid, 256, 0, s>>>(static_cast<const int8_t*>(packed), codes, rows, K);
+      else
+        unpack_b200_weight_kernel<<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(packed), codes,
+                                                       rows, K);
       break;
     case B200W4A4_CODES_WEIGHT_V1:
       if ((rows % 128) != 0) return B200W4A4_ESHAPE;
@@ -794,6 +827,13 @@ int b200w4a4_check_device(int device) {
   }
   cudaSetDevice(prev);
   return rc;
+}
+
+int b200w4a4_set_weight_staging(int bits) {
+  if (bits != 0 && bits != 4 && bits != 8) return B200W4A4_EINVAL;
+  const int prev = current_weight_staging();
+  if (bits != 0) g_weight_staging.store(bits, std::memory_order_relaxed);
+  return prev;
 }
 
 int b200w4a4_last_device_status(int device) {

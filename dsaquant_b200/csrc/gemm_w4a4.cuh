@@ -38,9 +38,6 @@
 #ifndef B200W4A4_OPT_FENCE_KB0
 #define B200W4A4_OPT_FENCE_KB0 1
 #endif
-#ifndef B200W4A4_ABL_W8
-#define B200W4A4_ABL_W8 0
-#endif
 
 namespace b200w4a4 {
 
@@ -53,7 +50,10 @@ enum : int {
   DEV_TIMEOUT_EPILOGUE = 104,
 };
 
-template <int CG>
+// W8: the weight operand is already int8 in global memory (every byte 16 * code, written by the
+// load-time expansion) and TMA stages it straight into the tile the tensor core reads: no packed
+// ring, no unpack warps' work, one more main-ring stage -- at twice the weight bytes in HBM and L2.
+template <int CG, bool W8 = false>
 struct GemmCfg {
   static constexpr int BM = 128;                 // rows of A per CTA
   static constexpr int BN = 256;                 // output columns per tile
@@ -65,12 +65,16 @@ struct GemmCfg {
   // Main ring: one stage = an A tile (TMA) + an unpacked weight tile; released by one MMA commit.
   // Packed weight tiles live in a second, shallower ring that is released as soon as they have
   // been unpacked.
-  static constexpr int S = (CG == 1) ? 3 : 5;
-  static constexpr int SB = (CG == 1) ? 3 : 4;
+  static constexpr int S = (CG == 1) ? (W8 ? 4 : 3) : (W8 ? 6 : 5);
+  static constexpr int SB = W8 ? 0 : ((CG == 1) ? 3 : 4);
   static constexpr int STAGE_BYTES = A_BYTES + BU_BYTES;
-  static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16 per epilogue warp
+  static constexpr int EPI_BUF = 32 * 128;       // 32 rows x 64 fp16: one TMA store box
   static constexpr int EPI_WARPS = 8;             // two warps per TMEM lane quadrant, half the columns each
-  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF;
+  // Staging buffers per epilogue warp.  Two (a warp fills one while the TMA store of the other
+  // still reads shared memory) fit only by giving up the fifth main-ring stage; measured, that
+  // trade changed nothing at K = 1536 and cost 3-6 % at K >= 8960, so one buffer it is.
+  static constexpr int EPI_STAGES = 1;
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_STAGES * EPI_BUF;
   static constexpr int OFF_MAIN = 0;
   static constexpr int OFF_BP = OFF_MAIN + S * STAGE_BYTES;
   static constexpr int OFF_EPI = OFF_BP + SB * BP_BYTES;
@@ -244,11 +248,11 @@ __device__ __forceinline__ float epi_gelu_tanh(float x) {
   return 0.5f * x * (1.0f + tanhf(inner));
 }
 
-template <int CG, int EPI = EPI_NONE>
-__global__ void __launch_bounds__(GemmCfg<CG>::THREADS, 1)
+template <int CG, int EPI = EPI_NONE, bool W8 = false>
+__global__ void __launch_bounds__(GemmCfg<CG, W8>::THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ OutMaps tm_out, const GemmParams p) {
-  using C = GemmCfg<CG>;
+  using C = GemmCfg<CG, W8>;
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles want a 1024 B aligned base.
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -277,7 +281,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::S; ++s) {
-      ptx::mbar_init(bar_full(s), B200W4A4_ABL_W8 ? 1 : C::UNPACK_WARPS * CG + 1);  // unpack warps + the A producer
+      ptx::mbar_init(bar_full(s), W8 ? 1 : C::UNPACK_WARPS * CG + 1);  // unpack warps + the A producer
       ptx::mbar_init(bar_consumed(s), 1);                     // one MMA commit
     }
     for (int s = 0; s < C::SB; ++s) {
@@ -332,32 +336,32 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             break;
           }
           const uint32_t dst = smem_base + C::OFF_MAIN + pos.slot * C::STAGE_BYTES;
-#if B200W4A4_ABL_W8
-          const int n0w = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
-          if constexpr (CG == 1) {
-            ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES + C::BU_BYTES);
-            ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
-            ptx::tma_load_2d(dst + C::A_BYTES, &tm_w, bar_full(pos.slot), kb * C::BK, n0w);
+          if constexpr (W8) {
+            const int n0w = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
+            if constexpr (CG == 1) {
+              ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES + C::BU_BYTES);
+              ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
+              ptx::tma_load_2d(dst + C::A_BYTES, &tm_w, bar_full(pos.slot), kb * C::BK, n0w);
+            } else {
+              if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * (C::A_BYTES + C::BU_BYTES));
+              uint32_t remote = full_remote[0];
+  #pragma unroll
+              for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
+              ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
+              ptx::tma_load_2d_pair(dst + C::A_BYTES, &tm_w, remote, kb * C::BK, n0w);
+            }
           } else {
-            if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * (C::A_BYTES + C::BU_BYTES));
-            uint32_t remote = full_remote[0];
-#pragma unroll
-            for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
-            ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
-            ptx::tma_load_2d_pair(dst + C::A_BYTES, &tm_w, remote, kb * C::BK, n0w);
+            if constexpr (CG == 1) {
+              ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES);
+              ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
+            } else {
+              if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * C::A_BYTES);
+              uint32_t remote = full_remote[0];
+  #pragma unroll
+              for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
+              ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
+            }
           }
-#else
-          if constexpr (CG == 1) {
-            ptx::mbar_arrive_expect_tx(bar_full(pos.slot), C::A_BYTES);
-            ptx::tma_load_2d(dst, &tm_a, bar_full(pos.slot), kb * C::BK, m0);
-          } else {
-            if (leader) ptx::mbar_arrive_expect_tx(bar_full(pos.slot), 2 * C::A_BYTES);
-            uint32_t remote = full_remote[0];
-#pragma unroll
-            for (int s = 1; s < C::S; ++s) remote = (pos.slot == s) ? full_remote[s] : remote;
-            ptx::tma_load_2d_pair(dst, &tm_a, remote, kb * C::BK, m0);
-          }
-#endif
           pos.advance();
         }
       }
@@ -370,7 +374,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp == C::WARP_B_PRODUCER) {
     // ===================== TMA producer: packed int4 weights =====================
-    if (lane == 0 && !B200W4A4_ABL_W8) {
+    if (lane == 0 && !W8) {
       RingPos<C::SB> pos;
       bool alive = true;
 #if B200W4A4_OPT_L2HINT
@@ -476,7 +480,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t lo_off = (((c2 + 1) ^ row_x) << 4);
     RingPos<C::S> pos;
     RingPos<C::SB> bpos;
-    bool alive = !B200W4A4_ABL_W8;
+    bool alive = !W8;
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
       for (int kb = 0; kb < kblocks; ++kb) {
         if (!detail::wait_bar(bar_bp_full(bpos.slot), bpos.phase, wctx, DEV_TIMEOUT_UNPACK) ||
@@ -520,8 +524,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else {
     // ===================== epilogue =====================
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-    const uint32_t stage_buf = smem_base + C::OFF_EPI + (warp - C::WARP_EPI0) * C::EPI_BUF;
-    const uint32_t stage = stage_buf + 128u * lane;
+    const uint32_t stage_buf0 = smem_base + C::OFF_EPI + (warp - C::WARP_EPI0) * (C::EPI_STAGES * C::EPI_BUF);
     const uint32_t row_sw = static_cast<uint32_t>(lane & 7);
     uint32_t local_tile = 0;
     bool alive = true;
@@ -551,20 +554,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       // Warps e and e+4 share a lane quadrant and split the tile's columns.
       constexpr int CHUNKS = (C::BN / 32) / (C::EPI_WARPS / 4);
       const int c_first = ((warp - C::WARP_EPI0) >> 2) * CHUNKS;
-      // Two chunks are loaded from TMEM per step so the second load's latency hides behind the
-      // first chunk's arithmetic.
+      // A 64-column store box is filled by two consecutive 32-column chunks; boxes alternate
+      // between the warp's staging buffers.
       auto process = [&](uint32_t (&acc)[32], const int c) {
-        if (c == c_first + CHUNKS - 2) {
-          // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CG == 1)
-              ptx::mbar_arrive(bar_acc_free(ab));
-            else
-              ptx::mbar_arrive_cluster(bar_acc_free(ab), 0);
-          }
-        }
+        const uint32_t stage_buf = stage_buf0 + (C::EPI_STAGES == 2 ? (((c - c_first) >> 1) & 1) * C::EPI_BUF : 0);
+        const uint32_t stage = stage_buf + 128u * lane;
         const int col0 = n0 + 32 * c;
         const bool cols_valid = col0 < p.N;  // N is a multiple of 128: a 32-chunk is all in or all out
         uint4 packed4[4];
@@ -632,9 +626,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         if ((c & 1) == 0) {
-          // The previous TMA store must have finished reading the staging buffer; waiting here,
-          // after the arithmetic, lets that read overlap this chunk's dequantisation.
-          if (lane == 0) ptx::tma_store_wait_read<0>();
+          // The store that last used this staging buffer must have finished reading it (with two
+          // buffers that is the store before the previous one); waiting here, after the
+          // arithmetic, lets that read overlap this chunk's dequantisation.
+          if (lane == 0) ptx::tma_store_wait_read<C::EPI_STAGES - 1>();
           __syncwarp();
         }
         if (cols_valid) {
@@ -670,13 +665,31 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
       };
+      // TMEM reads run one chunk ahead of the arithmetic: while chunk c is dequantised and staged,
+      // the load of chunk c + 1 is in flight.
+      auto release_accumulator = [&]() {
+        // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 1)
+            ptx::mbar_arrive(bar_acc_free(ab));
+          else
+            ptx::mbar_arrive_cluster(bar_acc_free(ab), 0);
+        }
+      };
+      uint32_t acc_a[32], acc_b[32];
+      ptx::tmem_ld_32x32(taddr + 32u * c_first, acc_a);
 #pragma unroll 1
       for (int c = c_first; c < c_first + CHUNKS; c += 2) {
-        uint32_t acc_a[32], acc_b[32];
-        ptx::tmem_ld_32x32(taddr + 32u * c, acc_a);
+        ptx::tmem_ld_wait_for(acc_a);
         ptx::tmem_ld_32x32(taddr + 32u * (c + 1), acc_b);
-        ptx::tmem_ld_wait();
         process(acc_a, c);
+        ptx::tmem_ld_wait_for(acc_b);
+        if (c + 2 < c_first + CHUNKS)
+          ptx::tmem_ld_32x32(taddr + 32u * (c + 2), acc_a);
+        else
+          release_accumulator();
         process(acc_b, c + 1);
       }
     }

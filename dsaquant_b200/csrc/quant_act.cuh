@@ -365,6 +365,9 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
     }
   };
 
+  // The prologue's output is fp16 by definition, so it replaces the raw chunk in registers: the
+  // modulation vectors are read (and tanh evaluated) once, and the abs-max and the codes below
+  // work on the stored fp16 values exactly as the plain kernel does.
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
@@ -372,8 +375,11 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
     if (row_ok && c < nchunks) {
       float v[8];
       transformed(i, c, v);
+      __half2 h[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);  // exact: already fp16 values
+      ch[i].raw = *reinterpret_cast<const uint4*>(h);
+      ch[i].absmax(amax);
     }
   }
   amax = row_reduce<TPR, true>(amax, red[2], sub);
@@ -386,7 +392,7 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
     if (c < nchunks) {
       float v[8];
       uint32_t codes[8];
-      transformed(i, c, v);
+      ch[i].values(v);
       detail::chunk_codes(v, rq, codes);
       detail::store_codes<QOUT_INT8>(q, static_cast<size_t>(row), K, c, codes);
     }
@@ -472,7 +478,9 @@ inline cudaError_t launch_quant_act_pre(const __half* x, void* q, float* scale, 
     const unsigned grid = static_cast<unsigned>((static_cast<long long>(M) + ROWS - 1) / ROWS);  \
     quant_act_pre_rows_kernel<TPR, NCH, PRE><<<grid, 256, 0, stream>>>(x, q, scale, M, K, clip, pre); \
   } while (0)
-  if (nchunks <= 32 * 8) B200W4A4_QPLAUNCH(32, 8);
+  if (nchunks <= 32 * 6) B200W4A4_QPLAUNCH(32, 6);         // K = 1536
+  else if (nchunks <= 32 * 8) B200W4A4_QPLAUNCH(32, 8);
+  else if (nchunks <= 64 * 6) B200W4A4_QPLAUNCH(64, 6);    // K = 3072
   else if (nchunks <= 64 * 8) B200W4A4_QPLAUNCH(64, 8);
   else if (nchunks <= 128 * 5) B200W4A4_QPLAUNCH(128, 5);  // K = 5120
   else if (nchunks <= 128 * 8) B200W4A4_QPLAUNCH(128, 8);

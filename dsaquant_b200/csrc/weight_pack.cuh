@@ -165,7 +165,32 @@ repack_v1_to_b200_kernel(const uint32_t* __restrict__ v1, uint4* __restrict__ ou
   out[j] = o;
 }
 
+// Load-time expansion for the int8-staged GEMM variant: v1 codes -> row-major int8 [N,K] with every
+// byte equal to 16 * code (the value the unpack warps would otherwise produce in shared memory).
+// One thread per 8 consecutive k of a row (one v1 word in, 8 bytes out).
+__global__ void __launch_bounds__(256)
+expand_v1_to_int8_kernel(const uint32_t* __restrict__ v1, uint2* __restrict__ out, int N, int K) {
+  const size_t j = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  const int words_per_row = K >> 3;
+  if (j >= static_cast<size_t>(N) * words_per_row) return;
+  const int n = static_cast<int>(j / words_per_row);
+  const int k8 = static_cast<int>(j % words_per_row) << 3;
+  const uint32_t wv = v1[detail::v1_word_index(n, k8, K)];
+  uint2 o;
+  o.x = ((wv & 0xFu) << 4) | ((wv & 0xF0u) << 8) | ((wv & 0xF00u) << 12) | ((wv & 0xF000u) << 16);
+  const uint32_t hi = wv >> 16;
+  o.y = ((hi & 0xFu) << 4) | ((hi & 0xF0u) << 8) | ((hi & 0xF00u) << 12) | ((hi & 0xF000u) << 16);
+  out[j] = o;
+}
+
 // ---- test helpers: extract int8 codes [rows,K] ---------------------------------
+__global__ void __launch_bounds__(256)
+unpack_int8_weight_kernel(const int8_t* __restrict__ w8, int8_t* __restrict__ codes, int N, int K) {
+  const size_t j = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (j >= static_cast<size_t>(N) * K) return;
+  codes[j] = static_cast<int8_t>(w8[j] >> 4);   // arithmetic shift: exact, every byte is 16 * code
+}
+
 __global__ void __launch_bounds__(256)
 unpack_b200_weight_kernel(const uint8_t* __restrict__ wr, int8_t* __restrict__ codes, int N, int K) {
   const size_t j = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;

@@ -248,12 +248,13 @@ def _version_of(t: torch.Tensor) -> int:
 def prepare_b200_weight(qweight: torch.Tensor, wscales: torch.Tensor):
     """Load-time repack of one layer: (vdm_weight_packed, vdm_weight_scale_packed) ->
     (w_b200 u8 [N,K/2] in the TMA/tcgen05 staging layout, plain scale f16 [N]).  Cached."""
+    lib = _load_ext()
+    staging = _weight_staging(lib)
     key = (qweight.data_ptr(), _version_of(qweight), tuple(qweight.shape), qweight.device.index,
-           wscales.data_ptr(), _version_of(wscales))
+           wscales.data_ptr(), _version_of(wscales), staging)
     hit = _PREPARED.get(key)
     if hit is not None:
         return hit
-    lib = _load_ext()
     _require_cuda(qweight, "qweight")
     n, k2 = qweight.shape
     k = 2 * k2
@@ -262,7 +263,7 @@ def prepare_b200_weight(qweight: torch.Tensor, wscales: torch.Tensor):
     qw = qweight if qweight.is_contiguous() else qweight.contiguous()
     ws = wscales if wscales.is_contiguous() else wscales.contiguous()
     dev = qweight.device
-    w_b200 = torch.empty((n, k2), dtype=torch.uint8, device=dev)
+    w_b200 = torch.empty((n, lib.b200w4a4_repack_bytes(n, k) // n), dtype=torch.uint8, device=dev)
     w_scale = torch.empty((n,), dtype=torch.float16, device=dev)
     with _DeviceGuard(dev):
         rc = lib.b200w4a4_repack_weight(qw.data_ptr(), w_b200.data_ptr(), ws.data_ptr(),
@@ -271,6 +272,39 @@ def prepare_b200_weight(qweight: torch.Tensor, wscales: torch.Tensor):
     _PREPARED[key] = (w_b200, w_scale)
     weakref.finalize(qweight, _PREPARED.pop, key, None)
     return w_b200, w_scale
+
+
+_STAGING = None
+
+
+def _weight_staging(lib) -> int:
+    global _STAGING
+    if _STAGING is None:
+        _STAGING = lib.b200w4a4_set_weight_staging(0)   # 0: query only
+    return _STAGING
+
+
+def set_weight_staging(bits: int) -> int:
+    """How the GEMM stages weights: 4 = packed int4 in HBM, widened to int8 in shared memory (default);
+    8 = int8 in HBM (twice the weight bytes, no widening work in the GEMM).  Process-wide; weights
+    repacked under the other setting are repacked again on their next use.  Returns the previous value."""
+    global _STAGING
+    rc = _load_ext().b200w4a4_set_weight_staging(int(bits))
+    if rc < 0:
+        _lib.check(rc, "set_weight_staging")
+    _STAGING = int(bits)
+    return rc
+
+
+def release_b200_weight(qweight: torch.Tensor) -> int:
+    """Drops the cached repack of `qweight` (e.g. a layer that from now on is only evaluated as
+    part of a fused projection).  Returns the number of entries released; a later call with the
+    same tensor simply repacks again."""
+    ptr, dev = qweight.data_ptr(), qweight.device.index
+    dead = [k for k in _PREPARED if k[0] == ptr and k[3] == dev]
+    for k in dead:
+        _PREPARED.pop(k, None)
+    return len(dead)
 
 
 # --------------------------------------------------------------------------- forward ops

@@ -246,6 +246,19 @@ int b200w4a4_unpack_codes(const void* packed, int8_t* codes, int rows, int K, in
  * 256x256 tile (cta_group::2).  Returns the previous value, or EINVAL. */
 int b200w4a4_set_cta_group(int cta_group);
 
+/* Select how the GEMM stages the weight operand; returns the previous value, or EINVAL
+ * (0 only asks for the current value).
+ *   4 (default)  the weight stays packed int4 in HBM and L2; TMA stages packed tiles and warps
+ *                of the GEMM widen them to int8 in shared memory (tcgen05 has no s4 kind);
+ *   8            b200w4a4_repack_weight writes int8 [N,K] (every byte 16 * code) and TMA stages it
+ *                straight into the tile the tensor core reads: no widening work inside the GEMM
+ *                (measured +5 % on the Wan-14B shapes, +10 % at K = 1536) for twice the weight bytes.
+ * The choice is process-wide and decides the meaning of every `w_b200` pointer and the size
+ * b200w4a4_repack_bytes returns: make it before any weight is repacked.  The environment variable
+ * B200W4A4_WEIGHT_STAGING=int8 selects 8 at first use.  No counterpart in the reference, whose
+ * kernel feeds s4 operands to mma.sync directly (vdm_w4a4_kernel.cu:114-143). */
+int b200w4a4_set_weight_staging(int bits);
+
 /* Synchronises `device`, returns and clears its device status word:
  * 0, or the code (> 0) of the kernel role whose bounded wait ran out
  * (101-104: a role of the GEMM; 105: b200w4a4_wait_flags).  The word is a report

@@ -303,3 +303,40 @@ def test_concurrent_threads_and_streams(vdm):
     for i, (x16, qw, ws, b16, _, _) in enumerate(cases):
         ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)["out"]
         np.testing.assert_array_equal(results[i].view(np.uint16), ref.view(np.uint16))
+
+
+def test_fused_projection_holds_one_copy_of_its_weights(vdm):
+    """After the fused caches are built the member layers keep no copies of their own: their v1
+    buffers are row views of the concatenated tensors, and the per-layer repacks are released.
+    Memory in use stays what it was before fusing (it doubled when every copy was kept)."""
+    from dsaquant_b200.attention_qkv import get_qkv_projections, prepare_fused_projections
+
+    torch.manual_seed(4)
+    attn = _Attn(1536, False).cuda().half()
+    for name in ("to_q", "to_k", "to_v"):
+        ql = _make_quant(getattr(attn, name))
+        ql.enable_vdm_kernel_mode()
+        ql.prepare_b200_weights()                      # what the checkpoint loader does per layer
+        setattr(attn, name, ql)
+    x = torch.randn(1, 300, 1536, device="cuda", dtype=torch.float16)
+    with torch.no_grad():
+        want = [attn.to_q(x), attn.to_k(x), attn.to_v(x)]
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    weights = 3 * 1536 * 768                           # bytes of the three packed weights
+    attn.use_fused_qkv_kernel, attn.qkv_kernel_backend = True, "vdm"
+    prepare_fused_projections(attn)
+    torch.cuda.synchronize()
+    after = torch.cuda.memory_allocated()
+    assert after - before < 0.25 * weights, (before, after)
+    base = attn._vdm_qkv_weight_packed
+    for i, name in enumerate(("to_q", "to_k", "to_v")):
+        buf = getattr(attn, name).vdm_weight_packed
+        assert buf.data_ptr() == base.data_ptr() + i * 1536 * 768 and buf.shape == (1536, 768)
+        assert name + ".vdm_weight_packed" in attn.state_dict()
+    with torch.no_grad():
+        got = get_qkv_projections(attn, x, None)
+        again = attn.to_k(x)                           # a member evaluated on its own still works
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert torch.equal(again, want[1])

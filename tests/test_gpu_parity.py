@@ -232,3 +232,35 @@ def test_tensor_maps_are_reused_between_identical_launches(vdm):
     assert (h1 - h0, m1 - m0) == (3, 0)
     torch.cuda.synchronize()
     assert torch.equal(out, first)
+
+
+def test_int8_staged_weights_give_identical_results(vdm):
+    """B200W4A4_WEIGHT_STAGING=int8 / set_weight_staging(8): the load-time step writes int8 [N,K]
+    (16 * code) and the GEMM stages it with TMA instead of widening packed tiles in shared memory.
+    Codes, accumulators and outputs must be the ones of the default packed path, for both CTA groups,
+    a ragged M and every epilogue input the plain call takes."""
+    M, K, N = 777, 1536, 640
+    x16, w16, b16 = make_case(31, M, K, N)
+    ws = orc.weight_scale_absmax(w16)
+    qw, qweight, wscales = _v1_buffers(w16, ws)
+    ref = orc.linear_w4a4(x16, qw, ws, b16, 0.95)
+    prev = vdm.set_weight_staging(8)
+    try:
+        w8, w_scale = vdm.prepare_b200_weight(qweight, wscales)
+        assert tuple(w8.shape) == (N, K)
+        np.testing.assert_array_equal(w8.view(torch.int8).cpu().numpy(), qw.astype(np.int16) * 16)
+        np.testing.assert_array_equal(vdm.unpack_codes(w8, N, K, 1).cpu().numpy(), qw)
+        for cg in (2, 1):
+            old = vdm.set_cta_group(cg)
+            try:
+                out = vdm.linear_vdm_w4a4(_cuda(x16), qweight, wscales, _cuda(b16), 0.95)
+                qact, ascales, _ = vdm.quantize_activation_per_token(_cuda(x16), 0.95)
+                _, acc = vdm.linear_prequantized(qact, ascales, qweight, wscales, return_acc=True)
+            finally:
+                vdm.set_cta_group(old)
+            np.testing.assert_array_equal(out.cpu().numpy().view(np.uint16), ref["out"].view(np.uint16))
+            np.testing.assert_array_equal(acc.cpu().numpy(), ref["acc"])
+    finally:
+        vdm.set_weight_staging(prev)
+    out4 = vdm.linear_vdm_w4a4(_cuda(x16), qweight, wscales, _cuda(b16), 0.95)   # back on the packed path
+    np.testing.assert_array_equal(out4.cpu().numpy().view(np.uint16), ref["out"].view(np.uint16))

@@ -83,3 +83,56 @@ def test_reference_kernel_statistics_and_this_kernel_exact(ref, vdm):
     rel_ref = (torch.linalg.vector_norm(out_ref.float() - o) / torch.linalg.vector_norm(o)).item()
     assert out_ref.shape == (m, n) and rel_ref < 0.05
     print(f"reference kernel vs oracle: rel_l2 {rel_ref:.3e}, max_abs {(out_ref.float() - o).abs().max().item():.3e}")
+
+
+def test_exported_checkpoint_equals_reference_packer_layer_by_layer(ref, vdm, tmp_path):
+    """Exporter (dsaquant_b200/checkpoints/export.py): a multi-layer model in its full quantised
+    form (fp weights + wquantizer scales) -> vdm_w4a4_packed_v1 file.  Every layer's three buffers
+    in the file equal what the reference's own packer writes for the same weight and scale, and
+    the file loads back into a fresh model that evaluates like the exported one."""
+    import torch.nn as nn
+
+    from dsaquant_b200.checkpoints import export as ex
+    from dsaquant_b200.checkpoints import packed_checkpoint as pc
+    from dsaquant_b200.quantization.quant_linear import QuantLinear
+
+    qp = {"w": {"bit": 4, "sym": True, "granularity": "per_channel"}, "act": {"bit": 4, "sym": True}}
+    shapes = [(256, 128), (128, 256), (384, 128), (128, 384)]            # (N, K)
+
+    def build():
+        torch.manual_seed(0)
+        m = nn.Sequential(*[nn.Linear(k, n, bias=(i % 2 == 0)) for i, (n, k) in enumerate(shapes)])
+        for i in range(len(shapes)):
+            m[i] = QuantLinear(m[i], {"w": "lsq", "act": "dynamic"}, qp)
+        return m
+
+    # Full quantised state with unambiguous codes: weight = code * scale, scale = s * 2^-6.
+    rng = np.random.default_rng(3)
+    state, truth = {}, {}
+    for i, (n, k) in enumerate(shapes):
+        codes = rng.integers(-7, 8, size=(n, k), dtype=np.int8)
+        scale = (np.full(n, 2.0 ** -6, np.float32) * (1 + (np.arange(n) % 3))).astype(np.float16)
+        w = (codes.astype(np.float32) * scale.astype(np.float32)[:, None]).astype(np.float16)
+        state[f"{i}.weight"] = torch.from_numpy(w)
+        state[f"{i}.wquantizer.scale"] = torch.from_numpy(scale.astype(np.float32)).view(n, 1)
+        if i % 2 == 0:
+            state[f"{i}.bias"] = torch.from_numpy(rng.standard_normal(n).astype(np.float16))
+        truth[i] = (w, scale)
+    out = tmp_path / "packed.pt"
+    stats = ex.export_packed_checkpoint(build(), {"model": state}, str(out), metadata={"model": "synthetic"})
+    assert stats["layers"] == len(shapes)
+    ckpt = torch.load(out, map_location="cpu", weights_only=True)
+    assert pc.is_packed_checkpoint(ckpt) and ckpt["metadata"]["model"] == "synthetic"
+    for i, (w, scale) in truth.items():
+        r_q, r_sp, r_s = ref.pack_weight_with_scale(torch.from_numpy(w).cuda(), torch.from_numpy(scale).cuda())
+        assert torch.equal(ckpt["model"][f"{i}.vdm_weight_packed"], r_q.cpu())
+        assert torch.equal(ckpt["model"][f"{i}.vdm_weight_scale_packed"], r_sp.cpu())
+        assert torch.equal(ckpt["model"][f"{i}.vdm_weight_scale"], r_s.half().cpu())
+        assert f"{i}.weight" not in ckpt["model"]
+    fresh = build()
+    pc.load_packed_quantized_model(fresh, ckpt, quant_linear_cls=QuantLinear, dtype=torch.float16,
+                                   device=torch.device("cuda"))
+    x = torch.randn(70, 128, device="cuda", dtype=torch.float16)
+    w0, s0 = truth[0]
+    want = orc.linear_w4a4(x.cpu().numpy(), orc.quantize_weight(w0, s0), s0, state["0.bias"].numpy(), 0.95)["out"]
+    np.testing.assert_array_equal(fresh[0](x).cpu().numpy().view(np.uint16), want.view(np.uint16))

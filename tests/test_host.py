@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
 
     header = (ROOT / "include" / "b200w4a4.h").read_text()
     declared = set(re.findall(r"\b(b200w4a4_[a-z0-9_]+)\s*\(", header))
-    assert len(declared) == 27
+    assert len(declared) == 28
     lib = _lib.load()
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
@@ -410,3 +410,54 @@ def test_quantiser_fast_path_bracket_is_exact():
             assert np.abs(ya).max() <= 7                # no clamp needed on this path
         checked += x.size
     assert checked > 4_000_000
+
+
+def test_reference_fused_call_site_binds_against_this_package():
+    """The reference's fused-QKV call site (modules/attention.py, `_get_qkv_projections`) imports
+    names from vdm_infer.kernels.vdm_w4a4 and calls them with keyword arguments.  Read from a
+    DSAQuant checkout when one is present (skipped otherwise): after install_as_vdm_infer() every
+    imported name must resolve, and every call must bind against this package's signatures."""
+    import ast
+    import inspect
+    import sys
+
+    import dsaquant_b200
+    from harness.bench_cpu import reference_checkout
+
+    ref = reference_checkout()
+    if ref is None:
+        pytest.skip("no DSAQuant checkout (DSAQUANT_REFERENCE)")
+    src = (Path(ref) / "vdm_infer" / "models" / "wan_vdm" / "modules" / "attention.py").read_text()
+    fn = next(n for n in ast.walk(ast.parse(src)) if isinstance(n, ast.FunctionDef) and n.name == "_get_qkv_projections")
+    imported = {}
+    for node in ast.walk(fn):
+        if isinstance(node, ast.ImportFrom) and node.module and node.module.startswith("vdm_infer."):
+            for alias in node.names:
+                imported[alias.asname or alias.name] = (node.module, alias.name)
+    assert set(imported) >= {"linear_vdm_w4a4", "linear_vdm_w4a4_qkv"}
+
+    saved = {k: v for k, v in sys.modules.items() if k == "vdm_infer" or k.startswith("vdm_infer.")}
+    for k in saved:
+        del sys.modules[k]
+    try:
+        dsaquant_b200.install_as_vdm_infer()
+        resolved = {}
+        for local, (module, name) in imported.items():
+            mod = __import__(module, fromlist=[name])
+            resolved[local] = getattr(mod, name)
+        calls = 0
+        for node in ast.walk(fn):
+            if isinstance(node, ast.Call) and isinstance(node.func, ast.Name) and node.func.id in resolved:
+                sig = inspect.signature(resolved[node.func.id])
+                sig.bind(*[object()] * len(node.args), **{kw.arg: object() for kw in node.keywords if kw.arg})
+                calls += 1
+        assert calls >= 2
+        # the attributes the call site reads on the projection layers exist on this QuantLinear
+        from vdm_infer.quantization.quant_linear import QuantLinear
+        ql = QuantLinear(torch.nn.Linear(128, 128), {"w": "lsq", "act": "dynamic"}, {"w": {}, "act": {}})
+        for attr in ("kernel_clip_ratio", "_bias_half"):
+            assert hasattr(ql, attr)
+    finally:
+        for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
