@@ -83,6 +83,16 @@ __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRope
     r = rsqrtf(ss / static_cast<float>(a.D) + a.eps);
   }
   const float* cs_row = (a.cos_sin != nullptr) ? a.cos_sin + row * static_cast<long long>(a.head_dim) : nullptr;
+  // 8 consecutive columns = 4 rotation pairs of one head (head_dim is a multiple of 8).  A thread's
+  // chunks are TPR * 8 columns apart; when that is a whole number of heads they all sit at the same
+  // offset inside their head, and the (cos, sin) pairs are fetched once instead of once per chunk.
+  const bool cs_shared = (TPR * 8) % a.head_dim == 0;
+  float4 cs0 = make_float4(1.f, 0.f, 1.f, 0.f), cs1 = cs0;
+  if (cs_row != nullptr && cs_shared && row_ok && t < nchunks) {
+    const int j0 = (8 * t) % a.head_dim;
+    cs0 = __ldg(reinterpret_cast<const float4*>(cs_row + j0));
+    cs1 = __ldg(reinterpret_cast<const float4*>(cs_row + j0) + 1);
+  }
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int c = t + i * TPR;
@@ -103,10 +113,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const QkNormRope
       for (int j = 0; j < 4; ++j) y[j] = h[j];
     }
     if (cs_row != nullptr) {
-      // 8 consecutive columns = 4 rotation pairs of one head; head_dim is a multiple of 8.
-      const int j0 = (8 * c) % a.head_dim;
-      const float4 cs0 = __ldg(reinterpret_cast<const float4*>(cs_row + j0));
-      const float4 cs1 = __ldg(reinterpret_cast<const float4*>(cs_row + j0) + 1);
+      if (!cs_shared) {
+        const int j0 = (8 * c) % a.head_dim;
+        cs0 = __ldg(reinterpret_cast<const float4*>(cs_row + j0));
+        cs1 = __ldg(reinterpret_cast<const float4*>(cs_row + j0) + 1);
+      }
       const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z};
       const float sn[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
 #pragma unroll

@@ -32,7 +32,7 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-DEFAULT_ROUTE = "nccl"
+DEFAULT_ROUTE = "peer_stores"
 
 
 class Layout:
