@@ -14,6 +14,12 @@ exchange costs no extra pass and no extra launch on the producer side:
     4. attention reads set p of this rank
     5. signal done[p][me] = e on every rank           (ordered after the attention kernel)
 
+`rotated=True` changes where rows land: every rank's own shard sits at rows [0, capacity) of its own
+buffers and the peers' shards follow in ascending rank order from row `capacity` on (a softmax over
+keys does not care about their order).  Local and remote keys are then two contiguous ranges, so
+attention over the local range can run while the remote range is still arriving (`local_rows`
+needs no wait at all, `remote_rows` enqueues the waits).  Requires every rank to own rows.
+
 Every wait is bounded (b200w4a4_wait_flags): a peer that never arrives shows up as device status
 105, not as a hang.  Only plain loads and stores touch peer memory; no multicast loads.
 
@@ -80,7 +86,8 @@ def layout(base: int, capacity_rows: int, dim: int, group: int) -> RankMemory:
 
 class PeerKVExchange:
     def __init__(self, rank: int, members: Sequence[RankMemory], local: torch.Tensor, capacity_rows: int,
-                 dim: int, row0: int, dtype: torch.dtype = torch.bfloat16, timeout_ms: int = 1000):
+                 dim: int, row0: int, dtype: torch.dtype = torch.bfloat16, timeout_ms: int = 1000,
+                 shard_rows: Optional[Sequence[int]] = None):
         """rank: index of this rank inside the group; members[r]: rank r's memory as mapped here
         (members[rank] must describe `local`, this rank's own zero-initialised exchange memory, a
         uint8 tensor of exchange_bytes); row0: first row of this rank's shard."""
@@ -91,6 +98,8 @@ class PeerKVExchange:
         self.capacity, self.dim, self.row0, self.dtype = capacity_rows, dim, row0, dtype
         self.timeout_ms = timeout_ms
         self.device = local.device
+        self.rotated = False
+        self.shard_rows = list(shard_rows) if shard_rows is not None else None
         self.epoch = 0                      # blocks use epochs 1, 2, ...: the first two wait for -1 and 0, both met by the zero-initialised flags
         self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._lib = _lib.load()
@@ -110,6 +119,28 @@ class PeerKVExchange:
                        for p in range(2)]
         self._done = [view(mine.done[p], 4 * self.group, torch.int32, (self.group,)) for p in range(2)]
 
+    # ---- rotated placement -----------------------------------------------------------------------
+    def set_rotated(self, on: bool) -> None:
+        """Own shard first, peers after it (see the module text).  Switch only between blocks, on
+        every rank of the group alike."""
+        if on:
+            if self.shard_rows is None or len(self.shard_rows) != self.group or min(self.shard_rows) < 1:
+                raise ValueError("rotated placement needs the row count of every rank's shard, all non-empty")
+            per = self.capacity // self.group
+            if any(r > per for r in self.shard_rows) or any(r != per for r in self.shard_rows[:-1]):
+                raise ValueError("rotated placement expects equal shards except a shorter last one")
+        self.rotated = bool(on)
+
+    def _slot_row(self, sender: int, receiver: int) -> int:
+        """First row of `sender`'s shard inside `receiver`'s buffers."""
+        if not self.rotated:
+            return self.row0 if sender == self.rank else -1     # plain layout: the global row offset
+        per = self.capacity // self.group
+        if sender == receiver:
+            return 0
+        others = [x for x in range(self.group) if x != receiver]
+        return per * (1 + others.index(sender))
+
     # ---- one self-attention block ------------------------------------------------------------
     def begin_block(self) -> int:
         """Step 1: new epoch; waits until every rank has released the buffer set it will overwrite."""
@@ -125,8 +156,15 @@ class PeerKVExchange:
         p = self.epoch & 1
         if x.reshape(-1, x.shape[-1]).shape[0] + self.row0 > self.capacity:
             raise ValueError("shard does not fit the gather buffer")
+        if self.rotated:
+            # per-destination row offsets are folded into the destination addresses
+            pitch = self.dim * 2
+            dests = [m.kv[p][i] + self._slot_row(self.rank, r) * pitch for r, m in enumerate(self.members)]
+            row0 = 0
+        else:
+            dests, row0 = [m.kv[p][i] for m in self.members], self.row0
         aq.qk_norm_rope_push(
-            x, norm_weight, cos_sin, eps, head_dim, [m.kv[p][i] for m in self.members], self.dim, self.row0,
+            x, norm_weight, cos_sin, eps, head_dim, dests, self.dim, row0,
             self.dtype, flag_ptrs=[m.ready[p][i] for m in self.members], flag_index=self.rank, epoch=self.epoch,
             ticket=self.ticket)
 
@@ -138,6 +176,23 @@ class PeerKVExchange:
         for i in range(2):
             aq.wait_flags(self._ready[p][i][:n], self.epoch, self.timeout_ms)
         return self._kv[p][0][:rows], self._kv[p][1][:rows]
+
+    def local_rows(self):
+        """Rotated placement: this rank's own (K, V) rows of the current block.  They were written by
+        this rank's own push kernels, so stream order is all the synchronisation they need."""
+        p = self.epoch & 1
+        n = self.shard_rows[self.rank]
+        return self._kv[p][0][:n], self._kv[p][1][:n]
+
+    def remote_rows(self):
+        """Rotated placement: enqueues the bounded waits for every peer's K and V and returns the
+        peers' (K, V) rows as one contiguous range."""
+        p = self.epoch & 1
+        for i in range(2):
+            aq.wait_flags(self._ready[p][i], self.epoch, self.timeout_ms)
+        per = self.capacity // self.group
+        n = sum(r for x, r in enumerate(self.shard_rows) if x != self.rank)
+        return self._kv[p][0][per:per + n], self._kv[p][1][per:per + n]
 
     def end_block(self) -> None:
         """Step 5: after the attention kernel (stream order), release the buffer set on every rank."""
@@ -151,7 +206,8 @@ class PeerKVExchange:
     # ---- real peers ---------------------------------------------------------------------------
     @classmethod
     def from_symmetric_memory(cls, group, capacity_rows: int, dim: int, row0: int,
-                              dtype: torch.dtype = torch.bfloat16, timeout_ms: int = 1000) -> "PeerKVExchange":
+                              dtype: torch.dtype = torch.bfloat16, timeout_ms: int = 1000,
+                              shard_rows: Optional[Sequence[int]] = None) -> "PeerKVExchange":
         """Allocates the exchange memory with torch's symmetric memory on every rank of `group`
         (a torch.distributed process group on one NVLink domain) and maps the peers' copies."""
         import torch.distributed as dist
@@ -168,6 +224,6 @@ class PeerKVExchange:
         members = [layout(int(handle.buffer_ptrs[r]), capacity_rows, dim, world) for r in range(world)]
         if int(handle.buffer_ptrs[rank]) != local.data_ptr():
             members[rank] = layout(local.data_ptr(), capacity_rows, dim, world)
-        ex = cls(rank, members, local, capacity_rows, dim, row0, dtype, timeout_ms)
+        ex = cls(rank, members, local, capacity_rows, dim, row0, dtype, timeout_ms, shard_rows)
         ex._handle = handle                                # keeps the mappings alive
         return ex

@@ -242,6 +242,37 @@ class WanAttention(nn.Module):
         return o.transpose(1, 2).flatten(2, 3).to(dtype)
 
 
+_LSE_BACKEND = None
+
+
+def sdpa_with_lse(q, k, v):
+    """Library attention that also returns the log-sum-exp of every query row, [1,H,Lq] fp32 (what
+    merging attention over two disjoint key ranges needs).  q, k, v: [1,H,L,hd] bf16.  Uses the
+    cuDNN attention op when it accepts the call, else the flash op; both are torch library kernels."""
+    global _LSE_BACKEND
+    order = [_LSE_BACKEND] if _LSE_BACKEND else ["cudnn", "flash"]
+    err = None
+    for name in order:
+        try:
+            if name == "cudnn":
+                out = torch.ops.aten._scaled_dot_product_cudnn_attention(q, k, v, None, True, 0.0, False, False)
+            else:
+                out = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, False, False)
+            _LSE_BACKEND = name
+            return out[0], out[1].reshape(q.shape[0], q.shape[1], q.shape[2]).float()
+        except Exception as exc:  # try the next library kernel
+            err = exc
+    raise RuntimeError(f"no library attention kernel returned a log-sum-exp: {err}")
+
+
+def merge_attention(o1, l1, o2, l2):
+    """Attention over the union of two disjoint key sets from the two partial results:
+    out = o1 * exp(l1 - l) + o2 * exp(l2 - l) with l = logaddexp(l1, l2).  o: [1,H,L,hd], l: [1,H,L]."""
+    l = torch.logaddexp(l1, l2)
+    w1, w2 = torch.exp(l1 - l)[..., None], torch.exp(l2 - l)[..., None]
+    return (o1.float() * w1 + o2.float() * w2).to(o1.dtype)
+
+
 def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
     """`WanAttention.core` with the per-token glue in the library: RMSNorm across heads, RoPE and the
     bf16 cast of q and k run as one pass each (dsaquant_b200.attention_qkv.qk_norm_rope), v is cast
@@ -257,6 +288,26 @@ def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
     gather = group is not None and is_self
     exchange = getattr(attn, "kv_exchange", None) if gather else None
     _mark("glue")
+    if exchange is not None and exchange.rotated:
+        # Own rows first, peers after them: attention over the local keys runs while the peers'
+        # rows are still on their way, and the two partial results are merged by log-sum-exp.
+        exchange.begin_block()
+        exchange.push("v", v[0], None, None, eps, hd)
+        exchange.push("k", k[0], attn.norm_k.weight, cs, eps, hd)
+        qn = qk_norm_rope(q[0], attn.norm_q.weight, cs, eps, hd)
+        lq = qn.shape[0]
+        qh = qn.view(1, lq, heads, hd).transpose(1, 2)
+        _mark("sdpa")
+        k_loc, v_loc = exchange.local_rows()
+        o1, l1 = sdpa_with_lse(qh, k_loc.view(1, -1, heads, hd).transpose(1, 2), v_loc.view(1, -1, heads, hd).transpose(1, 2))
+        _mark("exchange_wait")
+        k_rem, v_rem = exchange.remote_rows()
+        _mark("sdpa")
+        o2, l2 = sdpa_with_lse(qh, k_rem.view(1, -1, heads, hd).transpose(1, 2), v_rem.view(1, -1, heads, hd).transpose(1, 2))
+        o = merge_attention(o1, l1, o2, l2)
+        exchange.end_block()
+        _mark("other")
+        return o.transpose(1, 2).reshape(1, lq, d)
     if exchange is not None:
         # The kernels that produce K and V store their rows into every rank's gather buffer.
         exchange.begin_block()
@@ -439,13 +490,18 @@ class WanDiT(nn.Module):
         m_total = self.cfg.tokens
         parts = sharding.row_partition(m_total, world)
         cap = sharding.shard_capacity(m_total, world) * world
-        ex = PeerKVExchange.from_symmetric_memory(group, cap, self.cfg.dim, parts[rank][0])
+        ex = PeerKVExchange.from_symmetric_memory(group, cap, self.cfg.dim, parts[rank][0],
+                                                  shard_rows=[e - s for s, e in parts])
         ex.senders = sum(1 for s, e in parts if e > s)
         return ex
 
-    def set_kv_exchange(self, exchange) -> None:
+    def set_kv_exchange(self, exchange, overlap: bool = False) -> None:
         """Route of the K/V exchange: a PeerKVExchange (fused kernel route only), or None for the
-        NCCL all-gathers."""
+        NCCL all-gathers.  overlap=True places own rows first in the gather buffers and splits the
+        attention into a local and a remote part so that the exchange hides behind the local part.
+        Collective in effect: switch it on every rank of the group alike, between steps."""
+        if exchange is not None:
+            exchange.set_rotated(overlap)
         for blk in self.blocks:
             blk.attn1.kv_exchange = exchange
             blk.attn1.kv_senders = None if exchange is None else exchange.senders

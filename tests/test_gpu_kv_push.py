@@ -196,3 +196,60 @@ def test_unread_timeout_does_not_cancel_later_gemms(mods):
     assert err.value.code == -7
     assert vdm.last_device_status() == 105            # still readable, cleared by this read
     vdm.check_device()                                # clean again
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_rotated_placement_puts_own_rows_first_emulated(mods, ranks):
+    """Rotated placement of PeerKVExchange (own shard at row 0, peers after it in ascending rank order):
+    on every emulated rank the local range is its own shard and the remote range is the other shards,
+    in order, without holes (the last shard is shorter); and attention over local + remote keys merged
+    by log-sum-exp equals attention over all keys in their natural order."""
+    aq, vdm = mods
+    from dsaquant_b200 import peer_exchange as px
+    from dsaquant_b200.sharding import row_partition, shard_capacity
+    from harness import wan_dit
+
+    D, heads, total = 512, 4, 1900
+    hd = D // heads
+    parts = row_partition(total, ranks)
+    rows = [e - s for s, e in parts]                  # 1024 + 876, or 512 x 3 + 364
+    assert min(rows) > 0 and rows[-1] < rows[0]
+    cap = shard_capacity(total, ranks) * ranks
+    mem = [torch.zeros(px.exchange_bytes(cap, D, ranks), dtype=torch.uint8, device="cuda") for _ in range(ranks)]
+    members = [px.layout(m.data_ptr(), cap, D, ranks) for m in mem]
+    group = [px.PeerKVExchange(r, members, mem[r], cap, D, parts[r][0], timeout_ms=200, shard_rows=rows) for r in range(ranks)]
+    for ex in group:
+        ex.set_rotated(True)
+    g = torch.Generator(device="cuda").manual_seed(10 + ranks)
+    for block in range(3):
+        k = torch.randn(total, D, generator=g, device="cuda").half()
+        v = torch.randn(total, D, generator=g, device="cuda").half()
+        want_k, want_v = k.to(torch.bfloat16), v.to(torch.bfloat16)
+        for ex in group:
+            ex.begin_block()
+        for r, ex in enumerate(group):
+            s, e = parts[r]
+            ex.push("v", v[s:e], None, None, 1e-6, hd)
+            ex.push("k", k[s:e], None, None, 1e-6, hd)
+        for r, ex in enumerate(group):
+            s, e = parts[r]
+            lk, lv = ex.local_rows()
+            rk, rv = ex.remote_rows()
+            others = torch.cat([want_k[a:b] for x, (a, b) in enumerate(parts) if x != r])
+            assert torch.equal(lk, want_k[s:e]) and torch.equal(lv, want_v[s:e])
+            assert torch.equal(rk, others) and rk.shape[0] == total - (e - s)
+            assert torch.equal(rv, torch.cat([want_v[a:b] for x, (a, b) in enumerate(parts) if x != r]))
+            if block == 0:
+                q = torch.randn(1, heads, 200, hd, generator=g, device="cuda").to(torch.bfloat16)
+                split = lambda t: t.view(1, -1, heads, hd).transpose(1, 2)
+                o1, l1 = wan_dit.sdpa_with_lse(q, split(lk), split(lv))
+                o2, l2 = wan_dit.sdpa_with_lse(q, split(rk), split(rv))
+                merged = wan_dit.merge_attention(o1, l1, o2, l2)
+                full = torch.nn.functional.scaled_dot_product_attention(q, split(want_k), split(want_v))
+                assert (merged.float() - full.float()).abs().max().item() < 2e-2
+                cos = torch.nn.functional.cosine_similarity(merged.float().flatten(), full.float().flatten(), dim=0)
+                assert cos.item() > 0.9999
+        for ex in group:
+            ex.end_block()
+    torch.cuda.synchronize()
+    assert vdm.last_device_status() == 0
