@@ -461,3 +461,31 @@ def test_reference_fused_call_site_binds_against_this_package():
         for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_cpu_arm_port_matches_the_reference_quantlinear(monkeypatch):
+    """The benchmark's CPU arm: with a DSAQuant checkout it times the reference's own QuantLinear, without
+    one the restatement under oracle/.  Where both exist they must compute the same thing (clip 1.0)."""
+    from harness import bench_cpu
+    from oracle.fakequant_cpu import fakequant_linear
+
+    layers = [("a", 128, 256), ("b", 256, 128)]
+    monkeypatch.setattr(bench_cpu, "reference_checkout", lambda: None)
+    port = bench_cpu.CpuArm(layers, 32, 1.0, port_fn=fakequant_linear)
+    assert port.kind == "port" and port.time(1, 0) > 0
+    with pytest.raises(RuntimeError):
+        bench_cpu.CpuArm(layers, 32, 1.0)              # neither a checkout nor a port: nothing to time
+    monkeypatch.undo()
+    if bench_cpu.reference_checkout() is None:
+        pytest.skip("no DSAQuant checkout (DSAQUANT_REFERENCE)")
+    ref = bench_cpu.CpuArm(layers, 32, 1.0, port_fn=fakequant_linear)
+    assert ref.kind == "reference"
+    with torch.no_grad():
+        for (x, ql), (x2, (w, ws, b)) in zip(ref.items, port.items):
+            assert torch.equal(x, x2)
+            ql.aquantizer.init = False
+            want = ql(x)
+            # the port takes the fp16-rounded channel scale of the packed format; give it the reference's own
+            got = fakequant_linear(x2, w, ql.wquantizer.scale.reshape(-1).float(), b, 1.0)
+            torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+    assert bench_cpu.sized_rows(layers, 2, 1, 1.0, port_fn=fakequant_linear, budget_s=1e-9, lo=64, hi=256) == 64
