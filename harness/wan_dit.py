@@ -595,7 +595,10 @@ def cfg_step(model: WanDiT, latent, timestep, text_cond, text_uncond, guidance: 
     mine = model(latent, timestep, text_cond if branch == 0 else text_uncond, group=branch_group)
     world = dist.get_world_size(world_group)
     both = torch.empty((world,) + mine.shape, dtype=mine.dtype, device=mine.device)
-    dist.all_gather_into_tensor(both, mine.contiguous(), group=world_group)
+    if mine.is_cuda:
+        dist.all_gather_into_tensor(both, mine.contiguous(), group=world_group)
+    else:  # CPU back-ends take the list form
+        dist.all_gather(list(both.unbind(0)), mine.contiguous(), group=world_group)
     half = world // 2
     cond, uncond = both[0], both[half]
     return uncond + guidance * (cond - uncond)

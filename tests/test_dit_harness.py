@@ -30,8 +30,18 @@ def _worker(rank, world, port, out_dir):
         full = model(latent, t, text)
         shard = model(latent, t, text, group=dist.group.WORLD)
         err = (full - shard).abs().max().item()
+        # CFG layout of the benchmark at 2 ranks: one branch per rank, predictions exchanged by one all-gather.
+        from harness import dit_step
+
+        layout = dit_step.Layout(dist, world, rank)
+        assert layout.branch == rank and layout.branch_group is None and layout.cfg_name() == "cfg2"
+        _, _, text_neg = wan_dit.synth_inputs(cfg, "cpu", seed=4, negative=True)
+        single = wan_dit.cfg_step(model, latent, t, text, text_neg.float())
+        split = wan_dit.cfg_step(model, latent, t, text, text_neg.float(), branch_group=layout.branch_group,
+                                 world_group=layout.world_group, branch=layout.branch)
+        cfg_err = (single - split).abs().max().item()
         with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
-            f.write(f"{err:.3e} {tuple(full.shape)}")
+            f.write(f"{err:.3e} {cfg_err:.3e} {tuple(full.shape)}")
     finally:
         dist.destroy_process_group()
 
@@ -42,9 +52,10 @@ def test_row_sharded_forward_matches_unsharded_gloo(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
-        err, shape = (tmp_path / f"rank{r}.txt").read_text().split(" ", 1)
+        err, cfg_err, shape = (tmp_path / f"rank{r}.txt").read_text().split(" ", 2)
         assert shape == "(1, 1056, 4)"
         assert float(err) < 2e-2          # bf16 SDPA with differently ordered key blocks
+        assert float(cfg_err) < 1e-5      # CFG branches on two ranks == both forwards on one
 
 
 def test_config_token_counts():
