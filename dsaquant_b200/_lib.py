@@ -32,6 +32,8 @@ SIGNATURES = {
     "b200w4a4_gemm_split": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b200w4a4_qk_norm_rope": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, ctypes.c_longlong, c_int, c_int, c_void_p]),
     "b200w4a4_qk_norm_rope_push": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong, c_void_p, c_int, ctypes.c_uint32, c_void_p, c_int, c_int, c_void_p]),
+    "b200w4a4_attn_merge": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_void_p]),
     "b200w4a4_wait_flags": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_int, c_void_p]),
     "b200w4a4_signal_flags": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
     "b200w4a4_linear_fused": (c_int, [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_size_t, c_int, c_int, c_int, c_float, c_void_p]),

@@ -203,6 +203,31 @@ def qk_norm_rope_push(x: torch.Tensor, norm_weight: Optional[torch.Tensor], cos_
     _lib.check(rc, "qk_norm_rope_push")
 
 
+def merge_attention(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor, lse2: torch.Tensor) -> torch.Tensor:
+    """Attention over the union of two disjoint key sets from its two partial results.
+    o1, o2: bf16 [1, H, L, hd] as attention kernels return them (memory order [L, H, hd], i.e. a
+    transposed view of an [L, H*hd] matrix); lse1, lse2: fp32 [1, H, L] (or [1, H, L, 1]).
+    Returns bf16 [L, H*hd] (contiguous):  o1 * w1 + o2 * w2 with w_i = exp(lse_i - logaddexp(lse1, lse2))."""
+    lib = _lib.load()
+    if o1.dtype != torch.bfloat16 or o2.dtype != torch.bfloat16 or not o1.is_cuda:
+        raise RuntimeError("merge_attention takes bf16 CUDA tensors")
+    _, h, l, hd = o1.shape
+    rows = []
+    for o in (o1, o2):
+        m = o.transpose(1, 2).reshape(l, h * hd)        # a view when the memory order is [L, H, hd]
+        if m.stride(1) != 1 or m.stride(0) % 8 or m.data_ptr() % 16:
+            m = m.contiguous()
+        rows.append(m)
+    ls = [t.reshape(h, l).float().contiguous() for t in (lse1, lse2)]
+    out = torch.empty((l, h * hd), dtype=torch.bfloat16, device=o1.device)
+    with torch.cuda.device(o1.device):
+        rc = lib.b200w4a4_attn_merge(rows[0].data_ptr(), rows[0].stride(0), rows[1].data_ptr(), rows[1].stride(0),
+                                     ls[0].data_ptr(), ls[1].data_ptr(), out.data_ptr(), l, h, hd,
+                                     torch.cuda.current_stream(o1.device).cuda_stream)
+    _lib.check(rc, "attn_merge")
+    return out
+
+
 def wait_flags(flags: torch.Tensor, epoch: int, timeout_ms: int = 1000) -> None:
     """Enqueues the bounded wait for `flags` (int32 [n <= 32], this GPU's memory) to reach `epoch`.
     A wait that runs out is reported by vdm_w4a4.last_device_status() == 105, not by a hang."""

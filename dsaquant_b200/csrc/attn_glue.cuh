@@ -220,6 +220,41 @@ inline cudaError_t launch_qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t str
   return cudaGetLastError();
 }
 
+// Attention over the union of two disjoint key sets from the two partial results (what a rank
+// computes when it attends to its own keys while the peers' keys are still arriving):
+//   out = o1 * w1 + o2 * w2,  w_i = exp(l_i - logaddexp(l1, l2)),
+// o_i bf16 [L, H*hd] (row pitch ld_i), l_i fp32 [H, L] log-sum-exp of the scaled scores, out bf16 [L, H*hd].
+// One thread per 8 consecutive columns (one head never straddles a chunk: hd is a multiple of 8).
+__global__ void __launch_bounds__(256)
+attn_merge_kernel(const __nv_bfloat16* __restrict__ o1, const __nv_bfloat16* __restrict__ o2,
+                  const float* __restrict__ lse1, const float* __restrict__ lse2,
+                  __nv_bfloat16* __restrict__ out, int L, int H, int hd, long long ld1, long long ld2) {
+  const int chunks = (H * hd) >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= static_cast<long long>(L) * chunks) return;
+  const long long l = idx / chunks;
+  const int c = static_cast<int>(idx % chunks);
+  const int h = (8 * c) / hd;
+  const float a = __ldg(lse1 + static_cast<long long>(h) * L + l);
+  const float b = __ldg(lse2 + static_cast<long long>(h) * L + l);
+  const float m = fmaxf(a, b);
+  const float e1 = __expf(a - m), e2 = __expf(b - m);
+  const float inv = 1.0f / (e1 + e2);
+  const float w1 = e1 * inv, w2 = e2 * inv;
+  const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(o1 + l * ld1 + 8 * c));
+  const uint4 r2 = __ldcs(reinterpret_cast<const uint4*>(o2 + l * ld2 + 8 * c));
+  const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+  const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&r2);
+  uint4 o;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f1 = __bfloat1622float2(p1[j]), f2 = __bfloat1622float2(p2[j]);
+    po[j] = __floats2bfloat162_rn(fmaf(f1.x, w1, f2.x * w2), fmaf(f1.y, w1, f2.y * w2));
+  }
+  *reinterpret_cast<uint4*>(out + l * static_cast<long long>(H * hd) + 8 * c) = o;
+}
+
 // flag[d][index] = value on up to 8 flag arrays (this GPU's and peer-mapped ones), ordered after
 // everything the stream ran before this kernel: "I am done reading" / "my part is complete".
 struct SignalArgs {

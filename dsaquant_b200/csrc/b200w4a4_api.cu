@@ -691,6 +691,26 @@ int b200w4a4_qk_norm_rope(const void* x_f16, long long x_ld, const void* norm_we
                                     out_dtype, out_ld, 0, nullptr, 0, 0u, nullptr, L, D, stream);
 }
 
+int b200w4a4_attn_merge(const void* o1_bf16, long long o1_ld, const void* o2_bf16, long long o2_ld,
+                        const float* lse1, const float* lse2, void* out_bf16, int L, int H, int head_dim,
+                        void* stream) {
+  if (o1_bf16 == nullptr || o2_bf16 == nullptr || lse1 == nullptr || lse2 == nullptr || out_bf16 == nullptr)
+    return B200W4A4_EINVAL;
+  if (L < 1 || H < 1 || head_dim < 8 || (head_dim % 8) != 0) return B200W4A4_ESHAPE;
+  const long long d = static_cast<long long>(H) * head_dim;
+  if (o1_ld < d || o2_ld < d) return B200W4A4_ESHAPE;
+  if (!aligned16(o1_bf16) || !aligned16(o2_bf16) || !aligned16(out_bf16) || (o1_ld % 8) != 0 || (o2_ld % 8) != 0)
+    return B200W4A4_EALIGN;
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200W4A4_OK) return rc;
+  const long long threads = static_cast<long long>(L) * (d / 8);
+  attn_merge_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o1_bf16), static_cast<const __nv_bfloat16*>(o2_bf16), lse1, lse2,
+      static_cast<__nv_bfloat16*>(out_bf16), L, H, head_dim, o1_ld, o2_ld);
+  return cudaGetLastError() == cudaSuccess ? B200W4A4_OK : B200W4A4_ECUDA;
+}
+
 int b200w4a4_wait_flags(const uint32_t* flags, int n, uint32_t epoch, int timeout_ms, void* stream) {
   if (flags == nullptr || n < 1 || n > 32 || timeout_ms < 1 || timeout_ms > 10000) return B200W4A4_EINVAL;
   DeviceState* st = nullptr;

@@ -304,10 +304,12 @@ def _core_fused(attn, q, k, v, is_self, freqs, group=None, m_total=None):
         k_rem, v_rem = exchange.remote_rows()
         _mark("sdpa")
         o2, l2 = sdpa_with_lse(qh, k_rem.view(1, -1, heads, hd).transpose(1, 2), v_rem.view(1, -1, heads, hd).transpose(1, 2))
-        o = merge_attention(o1, l1, o2, l2)
+        from dsaquant_b200.attention_qkv import merge_attention as merge_fused
+
+        o = merge_fused(o1, l1, o2, l2)                 # [Lq, D] bf16, one pass
         exchange.end_block()
         _mark("other")
-        return o.transpose(1, 2).reshape(1, lq, d)
+        return o.view(1, lq, d)
     if exchange is not None:
         # The kernels that produce K and V store their rows into every rank's gather buffer.
         exchange.begin_block()

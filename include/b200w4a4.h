@@ -197,6 +197,17 @@ int b200w4a4_qk_norm_rope_push(const void* x_f16, long long x_ld, const void* no
                                uint32_t* const* flags, int flag_index, uint32_t epoch,
                                unsigned int* ticket, int L, int D, void* stream);
 
+/* Merge of two partial attention results over disjoint key sets:
+ *   out = o1 * w1 + o2 * w2,  w_i = exp(lse_i - logaddexp(lse1, lse2))
+ * o1 / o2: bf16 [L, H*head_dim] with row pitches o1_ld / o2_ld (elements), lse1 / lse2: fp32 [H, L]
+ * (log-sum-exp of the scaled scores, as attention kernels report it), out: bf16 [L, H*head_dim].
+ * Lets a row-sharded rank attend to its own keys while its peers' keys are still arriving and
+ * fold the two results afterwards.  No counterpart in the reference (its sequence-parallel
+ * hooks are identity stubs, vdm_infer/models/wan_vdm/modules/attention.py:20-32). */
+int b200w4a4_attn_merge(const void* o1_bf16, long long o1_ld, const void* o2_bf16, long long o2_ld,
+                        const float* lse1, const float* lse2, void* out_bf16, int L, int H, int head_dim,
+                        void* stream);
+
 /* Enqueues a one-warp kernel that waits until flags[i] has reached `epoch` (wrap-around safe
  * comparison) for every i < n (n <= 32), for at most timeout_ms (1..10000).  A wait that runs out
  * records code 105 in the device status word (b200w4a4_last_device_status) and ends the kernel;

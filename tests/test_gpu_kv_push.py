@@ -245,6 +245,11 @@ def test_rotated_placement_puts_own_rows_first_emulated(mods, ranks):
                 o1, l1 = wan_dit.sdpa_with_lse(q, split(lk), split(lv))
                 o2, l2 = wan_dit.sdpa_with_lse(q, split(rk), split(rv))
                 merged = wan_dit.merge_attention(o1, l1, o2, l2)
+                # the library's one-pass merge kernel against the PyTorch formula
+                fused = aq.merge_attention(o1, l1, o2, l2)
+                assert fused.shape == (200, D) and fused.dtype == torch.bfloat16
+                want_m = merged.transpose(1, 2).reshape(200, D).float()
+                assert (fused.float() - want_m).abs().max().item() <= 2 ** -7 * want_m.abs().max().item()
                 full = torch.nn.functional.scaled_dot_product_attention(q, split(want_k), split(want_v))
                 assert (merged.float() - full.float()).abs().max().item() < 2e-2
                 cos = torch.nn.functional.cosine_similarity(merged.float().flatten(), full.float().flatten(), dim=0)
