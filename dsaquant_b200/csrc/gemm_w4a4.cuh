@@ -31,14 +31,6 @@
 
 #include "ptx.cuh"
 
-// Build-time switches used while measuring variants (scratch builds only).
-#ifndef B200W4A4_OPT_L2HINT
-#define B200W4A4_OPT_L2HINT 1
-#endif
-#ifndef B200W4A4_OPT_FENCE_KB0
-#define B200W4A4_OPT_FENCE_KB0 1
-#endif
-
 namespace b200w4a4 {
 
 // Device status codes written by a kernel whose bounded wait ran out.
@@ -377,10 +369,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (lane == 0 && !W8) {
       RingPos<C::SB> pos;
       bool alive = true;
-#if B200W4A4_OPT_L2HINT
       // Weights are re-read by every row tile: ask L2 to keep them while outputs stream through.
       const uint64_t keep = ptx::l2_policy_evict_last();
-#endif
       for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step) {
         int mt, nt;
         tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
@@ -392,13 +382,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             break;
           }
           ptx::mbar_arrive_expect_tx(bar_bp_full(pos.slot), C::BP_BYTES);
-#if B200W4A4_OPT_L2HINT
           ptx::tma_load_2d_hint(smem_base + C::OFF_BP + pos.slot * C::BP_BYTES, &tm_w,
                                 bar_bp_full(pos.slot), kb * (C::BK / 2), n0, keep);
-#else
-          ptx::tma_load_2d(smem_base + C::OFF_BP + pos.slot * C::BP_BYTES, &tm_w,
-                           bar_bp_full(pos.slot), kb * (C::BK / 2), n0);
-#endif
           pos.advance();
         }
       }
@@ -442,17 +427,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               break;
             }
             tmem_d = tmem_base + ab * C::BN;
-#if B200W4A4_OPT_FENCE_KB0
             ptx::tc_fence_after_sync();  // orders the epilogue's TMEM reads before this tile's MMAs
-#endif
           }
           if (!detail::wait_bar(bar_full(s), phase, wctx, DEV_TIMEOUT_MMA)) {
             running = false;
             break;
           }
-#if !B200W4A4_OPT_FENCE_KB0
-          ptx::tc_fence_after_sync();
-#endif
           // +32 bytes along K inside the 128B swizzle row = +2 in the (addr >> 4) field.
           const uint32_t a_lo = a_lo0 + s * (C::STAGE_BYTES >> 4), b_lo = b_lo0 + s * (C::STAGE_BYTES >> 4);
           ptx::mma_i8_ss_lohi<CG>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, kb > 0 ? 1u : 0u);
@@ -528,11 +508,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t row_sw = static_cast<uint32_t>(lane & 7);
     uint32_t local_tile = 0;
     bool alive = true;
-#if B200W4A4_OPT_L2HINT
     // The output is written once and not read by this kernel: evict it first, so that it does
     // not push the weights (re-read by every row tile) out of L2.
     const uint64_t stream_out = ptx::l2_policy_evict_first();
-#endif
     for (int tile = first_tile; tile < num_tiles && alive; tile += tile_step, ++local_tile) {
       int mt, nt;
       tile_coords<CG>(tile, p.m_tiles, p.n_tiles, mt, nt);
@@ -648,17 +626,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               if constexpr (EPI == EPI_SPLIT) {
                 // seg_cols is a multiple of the 64-column store box, so a box lies in one segment.
                 const int sgm = c_store / p.seg_cols;
-#if B200W4A4_OPT_L2HINT
                 ptx::tma_store_2d_hint(&tm_out.seg[sgm], stage_buf, c_store - sgm * p.seg_cols, m0, stream_out);
-#else
-                ptx::tma_store_2d(&tm_out.seg[sgm], stage_buf, c_store - sgm * p.seg_cols, m0);
-#endif
               } else {
-#if B200W4A4_OPT_L2HINT
                 ptx::tma_store_2d_hint(&tm_out.seg[0], stage_buf, c_store, m0, stream_out);
-#else
-                ptx::tma_store_2d(&tm_out.seg[0], stage_buf, c_store, m0);
-#endif
               }
             }
             ptx::tma_store_commit();
