@@ -373,9 +373,10 @@ def main() -> None:
         for i, L in enumerate(layers):
             groups.setdefault(L["k"], []).append(i)
 
+        plan = [(hx[k], [host_layers[i] for i in idx], [hout[i] for i in idx]) for k, idx in groups.items()]
+
         def step_e2e():
-            for k, idx in groups.items():
-                pipe.run(hx[k], [host_layers[i] for i in idx], [hout[i] for i in idx], CLIP)
+            pipe.run_groups(plan, CLIP)
     else:
         hx, hout = {}, []
 

@@ -64,44 +64,55 @@ class HostLinearPipeline:
             clip_ratio: float = 1.0) -> None:
         """x_host [M,K] (pinned for real overlap), outs_host[i] [M,N_i] fp16 (pinned).  Returns after
         enqueueing; call synchronize() (or torch.cuda.synchronize()) before reading outs_host."""
-        m, k = x_host.shape
-        assert x_host.dtype == self.act_dtype and k <= self.k_max and x_host.is_contiguous()
-        for L, o in zip(layers, outs_host):
-            assert L.k == k and o.shape == (m, L.n) and L.n <= self.n_max and o.dtype == torch.float16
+        self.run_groups([(x_host, layers, outs_host)], clip_ratio)
+
+    @torch.no_grad()
+    def run_groups(self, groups: Sequence[tuple], clip_ratio: float = 1.0) -> None:
+        """Several (x_host, layers, outs_host) groups, each as in run(), in one pipelined sequence: the
+        copies and kernels of a group's first chunks overlap the tail of the group before it instead
+        of waiting for it to drain (a step of a model is usually a few such groups, one per distinct
+        activation matrix)."""
+        for x_host, layers, outs_host in groups:
+            m, k = x_host.shape
+            assert x_host.dtype == self.act_dtype and k <= self.k_max and x_host.is_contiguous()
+            for L, o in zip(layers, outs_host):
+                assert L.k == k and o.shape == (m, L.n) and L.n <= self.n_max and o.dtype == torch.float16
         self._ensure_out_events()
         cur = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_cmp, self.s_out):
             s.wait_stream(cur)
         dcode = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[self.act_dtype]
-        for r0 in range(0, m, self.chunk_rows):
-            rows = min(self.chunk_rows, m - r0)
-            xb = self._xslot % self.depth
-            self._xslot += 1
-            xv = self.xbuf[xb][: rows * k].view(rows, k)
-            with torch.cuda.stream(self.s_in):
-                self.s_in.wait_event(self.ev_x_free[xb])          # last compute on this x buffer is done
-                xv.copy_(x_host[r0:r0 + rows], non_blocking=True)
-                self.ev_in[xb].record(self.s_in)
-            for L, o_host in zip(layers, outs_host):
-                ob = self._slot % self.depth
-                self._slot += 1
-                ov = self.obuf[ob][: rows * L.n].view(rows, L.n)
+        for x_host, layers, outs_host in groups:
+            m, k = x_host.shape
+            for r0 in range(0, m, self.chunk_rows):
+                rows = min(self.chunk_rows, m - r0)
+                xb = self._xslot % self.depth
+                self._xslot += 1
+                xv = self.xbuf[xb][: rows * k].view(rows, k)
+                with torch.cuda.stream(self.s_in):
+                    self.s_in.wait_event(self.ev_x_free[xb])          # last compute on this x buffer is done
+                    xv.copy_(x_host[r0:r0 + rows], non_blocking=True)
+                    self.ev_in[xb].record(self.s_in)
+                for L, o_host in zip(layers, outs_host):
+                    ob = self._slot % self.depth
+                    self._slot += 1
+                    ov = self.obuf[ob][: rows * L.n].view(rows, L.n)
+                    with torch.cuda.stream(self.s_cmp):
+                        self.s_cmp.wait_event(self.ev_in[xb])
+                        self.s_cmp.wait_event(self.ev_o_free[ob])     # previous D2H from this out buffer is done
+                        rc = self.lib.b200w4a4_linear(
+                            xv.data_ptr(), dcode, L.w_b200.data_ptr(), L.w_scale.data_ptr(),
+                            L.bias.data_ptr() if L.bias is not None else None, ov.data_ptr(),
+                            self.work.data_ptr(), self.ws_bytes, rows, L.n, k, float(clip_ratio),
+                            ctypes.c_void_p(self.s_cmp.cuda_stream))
+                        _lib.check(rc, "linear")
+                        self.ev_cmp[ob].record(self.s_cmp)
+                    with torch.cuda.stream(self.s_out):
+                        self.s_out.wait_event(self.ev_cmp[ob])
+                        o_host[r0:r0 + rows].copy_(ov, non_blocking=True)
+                        self.ev_o_free[ob].record(self.s_out)
                 with torch.cuda.stream(self.s_cmp):
-                    self.s_cmp.wait_event(self.ev_in[xb])
-                    self.s_cmp.wait_event(self.ev_o_free[ob])     # previous D2H from this out buffer is done
-                    rc = self.lib.b200w4a4_linear(
-                        xv.data_ptr(), dcode, L.w_b200.data_ptr(), L.w_scale.data_ptr(),
-                        L.bias.data_ptr() if L.bias is not None else None, ov.data_ptr(),
-                        self.work.data_ptr(), self.ws_bytes, rows, L.n, k, float(clip_ratio),
-                        ctypes.c_void_p(self.s_cmp.cuda_stream))
-                    _lib.check(rc, "linear")
-                    self.ev_cmp[ob].record(self.s_cmp)
-                with torch.cuda.stream(self.s_out):
-                    self.s_out.wait_event(self.ev_cmp[ob])
-                    o_host[r0:r0 + rows].copy_(ov, non_blocking=True)
-                    self.ev_o_free[ob].record(self.s_out)
-            with torch.cuda.stream(self.s_cmp):
-                self.ev_x_free[xb].record(self.s_cmp)
+                    self.ev_x_free[xb].record(self.s_cmp)
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_cmp)
 

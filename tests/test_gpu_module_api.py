@@ -211,6 +211,20 @@ def test_host_pipeline_matches_direct_call(vdm):
         pipe.synchronize()
         for o, d in zip(outs, direct):
             assert torch.equal(o, d.cpu())
+    # two groups with different widths in one pipelined sequence (no drain between them)
+    x2_16, w_c, b_c = make_case(33, 700, 1024, 256)
+    packed, scale_packed, _ = vdm.quantize_weight_per_channel(torch.from_numpy(w_c).cuda())
+    layer_c = HostLinearLayer(packed, scale_packed, torch.from_numpy(b_c).cuda())
+    direct_c = vdm.linear_vdm_w4a4(torch.from_numpy(x2_16).cuda(), packed, scale_packed, None, 0.95,
+                                   bias_half=torch.from_numpy(b_c).cuda())
+    x2_host = torch.from_numpy(x2_16).pin_memory()
+    out_c = torch.empty(700, 256, dtype=torch.float16).pin_memory()
+    for o in outs:
+        o.zero_()
+    pipe.run_groups([(x_host, layers, outs), (x2_host, [layer_c], [out_c])], 0.95)
+    pipe.synchronize()
+    for o, d in zip(outs + [out_c], direct + [direct_c]):
+        assert torch.equal(o, d.cpu())
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
