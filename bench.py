@@ -194,7 +194,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=M_TOKENS)
     ap.add_argument("--sustain-seconds", type=float, default=2.5, help="length of the sustained leg (0: skip)")
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--e2e-chunk-rows", type=int, default=2048)
+    ap.add_argument("--e2e-chunk-rows", type=int, default=4096)
     ap.add_argument("--e2e-depth", type=int, default=3)
     ap.add_argument("--cpu-rows", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
