@@ -54,7 +54,9 @@ from harness.bench_common import (CLIP, DEFAULT_WORKLOAD, INT8_NOMINAL_TOPS, M_T
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one QKV-shaped GEMM launch at M = 32760, scaled
 # from the ncu capture summarised in profiles/ (M = 8192 case; traffic grows in proportion to M).
-GEMM_DRAM_TRAFFIC_BYTES = {"wan14b_linear_set_M32760": int(409.7e6 * 32760 / 8192)}
+GEMM_DRAM_TRAFFIC_BYTES = {"wan14b_linear_set_M32760": int((193.1e6 + 208.1e6) * 32760 / 8192),   # QKV 5120->15360
+                           "wan13b_linear_set_M32760": int((16.2e6 + 75.5e6) * 32760 / 8192)}     # QKV 1536->4608: reads + the full output
+# (at K = 1536 the 75.5 MB output was still in L2 when the captured launch ended: ncu saw 17.7 MB written)
 
 
 def base_config(workload: str, m: int, world: int, cta_group: int) -> dict:
