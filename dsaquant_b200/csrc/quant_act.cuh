@@ -100,11 +100,13 @@ struct Chunk<__nv_bfloat16> {
       v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
   }
+  // packed maxima, as for fp16: the maximum of bf16 values is one of them
   __device__ __forceinline__ void absmax(float& m) const {
-    float v[8];
-    values(v);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(v[e]));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    __nv_bfloat162 a = __hmax2(__habs2(h[0]), __habs2(h[1]));
+    __nv_bfloat162 b = __hmax2(__habs2(h[2]), __habs2(h[3]));
+    a = __hmax2(a, b);
+    m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
   }
 };
 
