@@ -5,7 +5,8 @@ Meant for profiler captures (a few hundred MB on the device, a handful of launch
 timing of a single shape:
 
     python harness/kernel_case.py gemm  --m 8192 --k 5120 --n 15360 [--cta-group 2] [--iters 2]
-    python harness/kernel_case.py quant --m 8192 --k 5120
+    python harness/kernel_case.py quant --m 8192 --k 5120 [--prologue layernorm_mod|gelu_tanh]
+    python harness/kernel_case.py gemm  --m 8192 --k 5120 --n 15360 --weight-staging int8
     python harness/kernel_case.py glue  --m 16384 --k 5120 --heads 40      # qk_norm_rope, k = model width
 
 `gemm` launches the quantiser and the GEMM `--iters` times each (the quantiser fills the codes the
@@ -30,6 +31,8 @@ def main() -> None:
     ap.add_argument("--cta-group", type=int, default=2)
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--weight-staging", default="int4", choices=["int4", "int8"])
+    ap.add_argument("--prologue", default="none", choices=["none", "layernorm_mod", "gelu_tanh"])
     args = ap.parse_args()
 
     import torch
@@ -39,6 +42,8 @@ def main() -> None:
 
     lib = _lib.load()
     vdm.set_cta_group(args.cta_group)
+    if args.weight_staging == "int8":
+        vdm.set_weight_staging(8)
     M, K, N = args.m, args.k, args.n
     torch.manual_seed(0)
     s = torch.cuda.current_stream().cuda_stream
@@ -48,16 +53,26 @@ def main() -> None:
     if args.kernel in ("gemm", "quant"):
         qact = torch.empty(M, K, device="cuda", dtype=torch.int8)
         asc = torch.empty(M, device="cuda", dtype=torch.float32)
+        mod = torch.randn(K, device="cuda", dtype=torch.float32) * 0.02
         if args.kernel == "gemm":
-            wq = torch.randint(0, 256, (N, K // 2), device="cuda", dtype=torch.uint8)   # repacked-layout bytes
+            if args.weight_staging == "int8":
+                wq = (torch.randint(-8, 8, (N, K), device="cuda", dtype=torch.int16) * 16).to(torch.int8)
+            else:
+                wq = torch.randint(0, 256, (N, K // 2), device="cuda", dtype=torch.uint8)   # repacked-layout bytes
             ws = (torch.rand(N, device="cuda") * 0.01 + 0.001).half()
             bias = torch.randn(N, device="cuda").half()
             out = torch.empty(M, N, device="cuda", dtype=torch.float16)
         for a, b in ev:
             if args.kernel == "quant":
                 a.record()
-            _lib.check(lib.b200w4a4_quantize_act(x.data_ptr(), 0, qact.data_ptr(), 0, asc.data_ptr(), M, K, 0.95, s),
-                       "quantize_act")
+            if args.prologue == "none":
+                _lib.check(lib.b200w4a4_quantize_act(x.data_ptr(), 0, qact.data_ptr(), 0, asc.data_ptr(), M, K, 0.95, s),
+                           "quantize_act")
+            else:
+                pre = {"gelu_tanh": 1, "layernorm_mod": 2}[args.prologue]
+                _lib.check(lib.b200w4a4_quantize_act_fused(x.data_ptr(), pre, mod.data_ptr(), mod.data_ptr(), 0, 1e-6,
+                                                           qact.data_ptr(), asc.data_ptr(), M, K, 0.95, s),
+                           "quantize_act_fused")
             if args.kernel == "gemm":
                 a.record()
                 _lib.check(lib.b200w4a4_gemm(qact.data_ptr(), asc.data_ptr(), wq.data_ptr(), ws.data_ptr(),
