@@ -49,13 +49,13 @@ struct PreArgs {
 namespace detail {
 
 // tanh-GELU evaluated in fp32 with the constants and operation order of the usual
-// "gelu(approximate='tanh')" definition, then rounded to fp16 like the tensor it replaces.
-__device__ __forceinline__ float gelu_tanh_f16(float x) {
+// "gelu(approximate='tanh')" definition; the caller rounds to fp16 like the tensor it replaces.
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
   const float kBeta = 0.7978845608028654f;  // sqrt(2/pi)
   const float kKappa = 0.044715f;
   const float x3 = x * x * x;
   const float inner = kBeta * (x + kKappa * x3);
-  return __half2float(__float2half_rn(0.5f * x * (1.0f + tanhf(inner))));
+  return 0.5f * x * (1.0f + tanhf(inner));
 }
 
 // A chunk is 8 consecutive values of a row, kept in registers in its storage format.
@@ -345,12 +345,13 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
     rstd = rsqrtf(var + pre.ln_eps);
   }
 
-  // The prologue's output for chunk i (values already rounded to fp16, held as fp32).
+  // The prologue's output for chunk i in fp32, before its final rounding to fp16 (done once, by the
+  // packing conversion below).
   auto transformed = [&](int i, int c, float (&v)[8]) {
     ch[i].values(v);
     if constexpr (PRE == PRE_GELU_TANH) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = detail::gelu_tanh_f16(v[e]);
+      for (int e = 0; e < 8; ++e) v[e] = detail::gelu_tanh_f32(v[e]);
     } else if constexpr (PRE == PRE_LAYERNORM_MOD) {
       const float* ms = pre.mod_scale + row * pre.mod_row_stride + 8 * c;
       const float* mh = pre.mod_shift + row * pre.mod_row_stride + 8 * c;
@@ -361,8 +362,7 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float n16 = __half2float(__float2half_rn((v[e] - mean) * rstd));   // layer norm, cast to fp16
-        const float m = __fadd_rn(__fmul_rn(n16, __fadd_rn(1.0f, sc[e])), sh[e]);  // * (1 + scale) + shift
-        v[e] = __half2float(__float2half_rn(m));
+        v[e] = __fadd_rn(__fmul_rn(n16, __fadd_rn(1.0f, sc[e])), sh[e]);          // * (1 + scale) + shift
       }
     }
   };
@@ -379,7 +379,7 @@ quant_act_pre_rows_kernel(const __half* __restrict__ x, void* __restrict__ q,
       transformed(i, c, v);
       __half2 h[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);  // exact: already fp16 values
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);  // the prologue's one rounding to fp16
       ch[i].raw = *reinterpret_cast<const uint4*>(h);
       ch[i].absmax(amax);
     }
