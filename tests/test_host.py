@@ -489,3 +489,84 @@ def test_cpu_arm_port_matches_the_reference_quantlinear(monkeypatch):
             got = fakequant_linear(x2, w, ql.wquantizer.scale.reshape(-1).float(), b, 1.0)
             torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
     assert bench_cpu.sized_rows(layers, 2, 1, 1.0, port_fn=fakequant_linear, budget_s=1e-9, lo=64, hi=256) == 64
+
+
+def test_reference_fused_call_site_runs_unchanged_against_these_modules(monkeypatch):
+    """Executes the reference's own `_get_qkv_projections` (source text read from a DSAQuant checkout,
+    compiled unchanged; skipped when there is none) on an attention object whose projections are
+    this package's QuantLinear layers holding vdm_w4a4_packed_v1 buffers.  The two kernel entry
+    points it imports are replaced by CPU stand-ins that decode the v1 buffers with the oracle, so the
+    test covers what the call site relies on: attribute names, the concatenation of v1 buffers along
+    dim 0, the cached `_vdm_qkv_*` / `_vdm_kv_*` attributes, bias handling and the split of the result."""
+    import ast
+    import sys
+
+    import dsaquant_b200
+    from dsaquant_b200.kernels import vdm_w4a4 as vdm
+    from dsaquant_b200.quantization.quant_linear import QuantLinear
+    from harness.bench_cpu import reference_checkout
+
+    ref = reference_checkout()
+    if ref is None:
+        pytest.skip("no DSAQuant checkout (DSAQUANT_REFERENCE)")
+    path = Path(ref) / "vdm_infer" / "models" / "wan_vdm" / "modules" / "attention.py"
+    src = path.read_text()
+    fn = next(n for n in ast.walk(ast.parse(src)) if isinstance(n, ast.FunctionDef) and n.name == "_get_qkv_projections")
+    ns = {"torch": torch}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), str(path), "exec"), ns)   # the reference's code, as it is
+    ref_get_qkv = ns["_get_qkv_projections"]
+
+    def cpu_linear(x, qweight, wscales, bias=None, clip_ratio=1.0, bias_half=None):
+        codes = orc.unpack_weight_v1(qweight.numpy())
+        ws = orc.unpack_wscale_v1(wscales.numpy())
+        b = bias_half if bias_half is not None else bias
+        shape = x.shape[:-1]
+        out = orc.linear_w4a4(x.reshape(-1, x.shape[-1]).numpy(), codes, ws,
+                              None if b is None else b.numpy(), clip_ratio)["out"]
+        return torch.from_numpy(out).reshape(*shape, -1)
+
+    def cpu_qkv(x, qp, qs, kp, ks, vp, vs, q_bias=None, k_bias=None, v_bias=None, clip_ratio=1.0,
+                w_qkv_packed=None, w_qkv_scale=None, qkv_bias_half=None):
+        assert w_qkv_packed is not None and w_qkv_scale is not None     # the call site passes its caches
+        return cpu_linear(x, w_qkv_packed, w_qkv_scale, None, clip_ratio, qkv_bias_half).split(qp.shape[0], dim=-1)
+
+    monkeypatch.setattr(vdm, "linear_vdm_w4a4", cpu_linear)
+    monkeypatch.setattr(vdm, "linear_vdm_w4a4_qkv", cpu_qkv)
+    saved = {k: v for k, v in sys.modules.items() if k == "vdm_infer" or k.startswith("vdm_infer.")}
+    for k in saved:
+        del sys.modules[k]
+    try:
+        dsaquant_b200.install_as_vdm_infer()
+        rng = np.random.default_rng(11)
+        D = 128
+        for cross in (False, True):
+            attn = _TinyAttn(D)
+            attn.cross_attention_dim_head = 64 if cross else None
+            separate = {}
+            for i, name in enumerate(("to_q", "to_k", "to_v")):
+                lin = getattr(attn, name)
+                ql = QuantLinear(lin, {"w": "lsq", "act": "dynamic"}, {"w": {}, "act": {}})
+                codes = rng.integers(-8, 8, size=(D, D), dtype=np.int8)
+                ws = (np.full(D, 2.0 ** -6, np.float32) * (1 + (np.arange(D) % 3))).astype(np.float16)
+                ql.register_buffer("vdm_weight_packed", torch.from_numpy(orc.pack_weight_v1(codes)))
+                ql.register_buffer("vdm_weight_scale_packed", torch.from_numpy(orc.pack_wscale_v1(ws, D)))
+                ql.register_buffer("vdm_weight_scale", torch.from_numpy(ws))
+                ql._bias_half = torch.from_numpy(rng.standard_normal(D).astype(np.float16)) if i != 1 else None
+                ql.use_vdm_kernel = True
+                setattr(attn, name, ql)
+                separate[name] = (codes, ws, ql._bias_half)
+            attn.use_fused_qkv_kernel, attn.qkv_kernel_backend = True, "vdm"
+            x = torch.from_numpy(rng.standard_normal((1, 37, D)).astype(np.float16))
+            ctx = torch.from_numpy(rng.standard_normal((1, 21, D)).astype(np.float16)) if cross else None
+            q, k, v = ref_get_qkv(attn, x, ctx)
+            for name, got, inp in (("to_q", q, x), ("to_k", k, ctx if cross else x), ("to_v", v, ctx if cross else x)):
+                codes, ws, b = separate[name]
+                want = orc.linear_w4a4(inp.reshape(-1, D).numpy(), codes, ws, None if b is None else b.numpy(),
+                                       attn.to_q.kernel_clip_ratio)["out"]
+                np.testing.assert_array_equal(got.reshape(-1, D).numpy().view(np.uint16), want.view(np.uint16))
+            cache = "_vdm_kv_weight_packed" if cross else "_vdm_qkv_weight_packed"
+            assert getattr(attn, cache).shape == ((2 if cross else 3) * D, D // 2)
+    finally:
+        for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
