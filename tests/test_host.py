@@ -570,3 +570,69 @@ def test_reference_fused_call_site_runs_unchanged_against_these_modules(monkeypa
         for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_packed_checkpoint_files_interoperate_with_the_reference_modules(tmp_path):
+    """vdm_w4a4_packed_v1 files cross between the two implementations (CPU; needs a DSAQuant checkout,
+    skipped otherwise): a file written by this package's writer loads through the reference's
+    load_packed_quantized_model into the reference's QuantLinear, a file written by the reference's
+    writer loads through this package's loader, and both directions keep every buffer bit for bit."""
+    import importlib
+    import sys
+
+    from dsaquant_b200.checkpoints import packed_checkpoint as mine
+    from dsaquant_b200.quantization.quant_linear import QuantLinear as MyQL
+    from harness.bench_cpu import reference_checkout
+
+    ref = reference_checkout()
+    if ref is None:
+        pytest.skip("no DSAQuant checkout (DSAQUANT_REFERENCE)")
+    saved = {k: v for k, v in sys.modules.items() if k == "vdm_infer" or k.startswith("vdm_infer.")}
+    for k in saved:
+        del sys.modules[k]
+    sys.path.insert(0, ref)
+    try:
+        theirs = importlib.import_module("vdm_infer.checkpoints.packed_checkpoint")
+        RefQL = importlib.import_module("vdm_infer.quantization.quant_linear").QuantLinear
+        assert theirs.PACKED_CHECKPOINT_FORMAT == mine.PACKED_CHECKPOINT_FORMAT
+        assert tuple(theirs.VDM_BUFFER_SUFFIXES) == tuple(mine.VDM_BUFFER_SUFFIXES)
+        rng = np.random.default_rng(21)
+
+        def model_with(cls):
+            m = _TinyModel()
+            _quantize_blocks(m, cls)
+            return m
+
+        def load(module, cls, ckpt):
+            m = model_with(cls)
+            kw = dict(quant_linear_cls=cls, dtype=torch.float16, device=torch.device("cpu"), require_vdm_kernel=False)
+            if module is mine:
+                kw["repack_for_b200"] = False
+            missing, unexpected = module.load_packed_quantized_model(m, ckpt, **kw)
+            assert list(missing) == [] and list(unexpected) == []
+            return m
+
+        truth = {"format": mine.PACKED_CHECKPOINT_FORMAT, "metadata": {}, "model": _packed_state(model_with(MyQL), rng)}
+        # this package's writer -> the reference's loader and layer class
+        a = tmp_path / "mine.pt"
+        mine.save_packed_checkpoint(load(mine, MyQL, truth), str(a), metadata={"by": "b200"})
+        into_ref = load(theirs, RefQL, theirs.load_quant_checkpoint(str(a), None))
+        # the reference's writer -> this package's loader and layer class
+        b = tmp_path / "theirs.pt"
+        theirs.save_packed_checkpoint(into_ref, str(b), metadata={"by": "reference"})
+        into_mine = load(mine, MyQL, mine.load_quant_checkpoint(str(b), None))
+        for name in ("to_q", "to_k", "to_v"):
+            for suffix in mine.VDM_BUFFER_SUFFIXES:
+                want = truth["model"][f"blocks.0.{name}.{suffix}"]
+                assert torch.equal(getattr(getattr(into_ref.blocks[0], name), suffix), want)
+                assert torch.equal(getattr(getattr(into_mine.blocks[0], name), suffix), want)
+            assert getattr(into_ref.blocks[0], name).use_vdm_kernel and getattr(into_mine.blocks[0], name).use_vdm_kernel
+        fa, fb = torch.load(a, weights_only=True), torch.load(b, weights_only=True)
+        assert set(fa["model"]) == set(fb["model"])
+        for key in fa["model"]:
+            assert torch.equal(fa["model"][key], fb["model"][key]), key
+    finally:
+        sys.path.remove(ref)
+        for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
