@@ -160,6 +160,7 @@ def measure(model_name: str, steps: int, warmup: int, *, layers: int = 0, fused:
     model = wan_dit.build_model(cfg, device, seed=0, backend="kernel")
     torch.cuda.synchronize()
     build_s = time.time() - t0
+    model_gb = torch.cuda.memory_allocated(device) / 1e9
     model.set_fused(fused)
     latent, timestep, text = wan_dit.synth_inputs(cfg, device, seed=1)
     _, _, text_neg = wan_dit.synth_inputs(cfg, device, seed=2, negative=True)
@@ -207,6 +208,7 @@ def measure(model_name: str, steps: int, warmup: int, *, layers: int = 0, fused:
     result = {"model": cfg.name, "tokens": m, "layers": L, "dim": d, "ffn": f, "heads": cfg.heads,
               "n_gpus": world, "steps": steps, "warmup": warmup, "guidance": 5.0, "fused_elementwise": bool(fused),
               "attention": "bf16 SDPA (library)", "model_build_s": round(build_s, 1),
+              "model_memory_gb": round(model_gb, 2),
               "w4a4_linear_tera_ops_per_forward": per_fwd / 1e12}
     if ex_error:
         result["peer_stores_unavailable"] = ex_error

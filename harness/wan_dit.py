@@ -458,6 +458,11 @@ class WanDiT(nn.Module):
             for attn in (blk.attn1, blk.attn2):
                 attn.use_fused_qkv_kernel = True
                 attn.qkv_kernel_backend = "vdm"
+                # one copy of the fused projection's weights from the start (what enable_fused_qkv does
+                # for a model loaded from a packed checkpoint)
+                from dsaquant_b200.attention_qkv import prepare_fused_projections
+
+                prepare_fused_projections(attn)
         self.set_backend(backend)
 
     def set_backend(self, backend: str):
