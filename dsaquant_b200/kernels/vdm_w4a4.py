@@ -104,7 +104,20 @@ def build_config() -> dict:
     }
 
 
+_EXT = None
+
+
 def _load_ext():
+    """The loaded library.  Arch selection and loading run once; later calls are a global read (the
+    reference keeps its extension in a module-level singleton the same way, vdm_w4a4.py:19,130-133)."""
+    global _EXT
+    if _EXT is not None:
+        return _EXT
+    _EXT = _load_ext_once()
+    return _EXT
+
+
+def _load_ext_once():
     tag = _arch_tag(_detect_arch_list())
     if "sm100a" not in tag.split("_") and "sm100" not in tag.split("_"):
         raise RuntimeError(f"b200 W4A4 kernels target sm_100a only, selected arch is {tag!r}")
@@ -308,6 +321,12 @@ def release_b200_weight(qweight: torch.Tensor) -> int:
 
 
 # --------------------------------------------------------------------------- forward ops
+def _workspace_bytes(m: int, k: int) -> int:
+    """b200w4a4_linear_workspace_bytes(m, k) without the foreign call: codes and scales, each rounded
+    up to 256 bytes (checked against the library in tests/test_host.py)."""
+    return ((m * k + 255) & ~255) + ((m * 4 + 255) & ~255)
+
+
 def _linear_prepared(x_2d: torch.Tensor, w_b200: torch.Tensor, w_scale: torch.Tensor,
                      bias_h: Optional[torch.Tensor], clip_ratio: float) -> torch.Tensor:
     lib = _load_ext()
@@ -317,7 +336,7 @@ def _linear_prepared(x_2d: torch.Tensor, w_b200: torch.Tensor, w_scale: torch.Te
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     if m == 0:
         return out
-    ws_bytes = lib.b200w4a4_linear_workspace_bytes(m, k)
+    ws_bytes = _workspace_bytes(m, k)
     workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
     with _DeviceGuard(dev):
         rc = lib.b200w4a4_linear(
@@ -604,7 +623,7 @@ def linear_vdm_w4a4_fused(
                 gt.data_ptr() if gt is not None else None, g_stride, m, n, k, stream)
         _lib.check(rc, "gemm_fused")
         return out.view(*orig_shape, n)
-    ws_bytes = lib.b200w4a4_linear_workspace_bytes(m, k)
+    ws_bytes = _workspace_bytes(m, k)
     workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
     with _DeviceGuard(dev):
         rc = lib.b200w4a4_linear_fused(

@@ -636,3 +636,12 @@ def test_packed_checkpoint_files_interoperate_with_the_reference_modules(tmp_pat
         for k in [k for k in sys.modules if k == "vdm_infer" or k.startswith("vdm_infer.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_python_workspace_size_matches_the_library():
+    from dsaquant_b200 import _lib
+    from dsaquant_b200.kernels import vdm_w4a4 as vdm
+
+    lib = _lib.load()
+    for m, k in ((1, 64), (257, 1536), (300, 5120), (32760, 13824), (4095, 8960)):
+        assert vdm._workspace_bytes(m, k) == lib.b200w4a4_linear_workspace_bytes(m, k)
